@@ -1,0 +1,116 @@
+/* C ABI of libwgp_int8.so, the B200 (sm_100a) INT8 weight-linear library.
+ *
+ * Every entry point below replaces the entry point of the same name in the reference library
+ * (wgpkernels/int8/int8_gemm.cu of WGPKernels, ABI 11); the reference's Python module binds them with
+ * ctypes (wgpkernels/int8/__init__.py:73-89) and this library keeps names, argument order, argument
+ * meaning and error codes, so that module can load this file unchanged.
+ *
+ * Conventions (same as the reference):
+ *   - all pointers are device pointers owned by the caller unless stated; nothing is allocated here except
+ *     the private buffer of wq8_l2_flush();
+ *   - `stream` is a raw cudaStream_t of the CURRENT device; calls launch asynchronously and never synchronize;
+ *   - return value: 0 = launched, > 0 = a cudaError_t, -1 = bad dtype / act / group, -2 = bad operands,
+ *     -3 = unknown variant, -4 = bad segments;
+ *   - dtype: 0 = fp16, 1 = bf16, 2 = fp32 (quantizer inputs only, no input operation);
+ *   - act: 0 none, 1 rms_norm (act_weight: K values of x's dtype or NULL; eps), 2 swiglu (x rows hold
+ *     [gate (K) | value (K)]), 3 gelu (tanh approximation);
+ *   - group: ConvRot rotation group, one of 0 (none), 16, 64, 256;
+ *   - ldx: row stride of x in elements; rows of x are 16-byte aligned (8-byte for wq8_gemv_lines).
+ */
+#ifndef WQ8_H
+#define WQ8_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* wq8_stream_t; /* cudaStream_t */
+
+/* ABI version (11) and feature bits (bit 0: per-(n, 128-block of K) weight scales, variants 12-14).
+ * Replaces int8_gemm.cu:1349-1352. */
+int wq8_abi(void);
+int wq8_features(void);
+
+/* q (M, K) int8 and scale (M, ceil(K / 128)) fp32 of op(x): one scale per row and 128-element block of K.
+ * K multiple of 8; M at most 65535 per call is NOT required here (any M).  inv_rms: M floats of scratch, only
+ * read/written for rms_norm with K > 16384 (else may be NULL).  Replaces int8_gemm.cu:1936-1943. */
+int wq8_quantize_blocks(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, int dtype, int group, int act,
+                        const void* act_weight, float eps, float* inv_rms, wq8_stream_t stream);
+
+/* Row-wise INT8 of op(x): hi (M, K), scale (M) and, when lo is not NULL, the exact split
+ * op(x) ~= scale * (hi + lo / 254).  Replaces int8_gemm.cu:1404-1414. */
+int wq8_quantize(const void* x, int8_t* hi, int8_t* lo, float* scale, int m, int k, int64_t ldx, int dtype, int group, int act,
+                 const void* act_weight, float eps, wq8_stream_t stream);
+
+/* out (M, K) = op(x), rotated, rounded once to x's dtype (fp16 / bf16): the activation of the few-token
+ * paths.  Replaces int8_gemm.cu:1971-1977. */
+int wq8_transform_rows(const void* x, void* out, int m, int k, int64_t ldx, int dtype, int group, int act, const void* act_weight,
+                       float eps, wq8_stream_t stream);
+
+/* out (M, K) = ConvRot rotation of x in groups of 16 / 64 / 256, normalised, rounded once.
+ * Replaces int8_gemm.cu:1871-1876. */
+int wq8_rotate_groups(const void* x, void* out, int m, int k, int64_t ldx, int dtype, int group, wq8_stream_t stream);
+
+/* Y (M, N) = (A (M, K) * sa) @ (B (N, K) * sb).T + bias, or residual + rscale * (...), FP32 epilogue, one
+ * rounding to dtype (fp16 / bf16); y may be the residual.  K multiple of 16; A, B, residual, y contiguous.
+ * variant selects the mode (tile shapes are this library's own):
+ *   0, 2, 6  'row'      sa (M)               sb (N)
+ *   1, 7     'exact'    sa (M), a_lo given   sb (N)
+ *   10, 11   'block'    sa (M, ceil(K/128))  sb (N)
+ *   12, 13   'block+g'  sa (M, ceil(K/128))  sb (N, ceil(K/128))
+ *   14       'exact+g'  sa (M), a_lo given   sb (N, ceil(K/128))
+ * a_lo must be non-NULL exactly for variants 1, 7, 14 (else -2).  split: 0 = whole tiles, 1 = tiles may be
+ * split along K when they leave SMs idle.  workspace / counters: sizes from wq8_gemm_workspace(); counters
+ * must be zero on entry and are left zero.  sms: SM count of the device.  Replaces int8_gemm.cu:1648-1656. */
+int wq8_gemm(const int8_t* a, const int8_t* a_lo, const float* sa, const int8_t* b, const float* sb, const void* bias,
+             const void* residual, const void* rscale, void* y, int m, int n, int k, int dtype, int variant, int sms, int split,
+             int* workspace, int* counters, wq8_stream_t stream);
+
+/* sizes[0] = workspace bytes, sizes[1] = counter bytes of wq8_gemm with these arguments.
+ * Replaces int8_gemm.cu:1506-1528. */
+void wq8_gemm_workspace(int m, int n, int k, int variant, int sms, int split, int64_t* sizes);
+
+/* Default variant of the 'row' (hilo = 0) or 'exact' (hilo = 1) mode for a shape.  Replaces int8_gemm.cu:1564-1568. */
+int wq8_gemm_select(int m, int n, int k, int hilo, int sms);
+
+/* wq8_gemm of `count` (1 to 4) weights bs[s] (rows, K) of one input in one launch, outputs ys[s] (M, rows),
+ * rows a multiple of 8; per-channel weight scales only; no residual.  Replaces int8_gemm.cu:1663-1676. */
+int wq8_gemm_segments(const int8_t* a, const int8_t* a_lo, const float* sa, const int8_t* const* bs, const float* const* sbs,
+                      const void* const* biases, void* const* ys, int count, int rows, int m, int k, int dtype, int variant, int sms,
+                      int split, int* workspace, int* counters, wq8_stream_t stream);
+
+/* Weight-only INT8 for at most 32 unquantized tokens: Y = X @ (W * sw).T + bias (+ residual), FP32
+ * accumulation of exact products.  K multiple of 64.  slots / counters: sizes from wq8_small_workspace();
+ * counters zero on entry, left zero.  Replaces int8_gemm.cu:1752-1759 and :1693-1697. */
+int wq8_small(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
+              void* y, int m, int n, int k, int dtype, int sms, float* slots, int* counters, wq8_stream_t stream);
+void wq8_small_workspace(int m, int n, int k, int sms, int64_t* sizes);
+
+/* The same linear for one to four tokens, K multiple of 4, no workspace.  Replaces int8_gemm.cu:1851-1858. */
+int wq8_gemv_lines(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual,
+                   const void* rscale, void* y, int m, int n, int k, int dtype, wq8_stream_t stream);
+
+/* Reads `bytes` from a private cudaMalloc buffer on `stream` so that the next launch finds a cold L2 (tuner
+ * timing).  Returns nonzero when the buffer cannot be allocated.  wq8_l2_flush_release() frees it.
+ * Replaces int8_gemm.cu:1997-2016. */
+int wq8_l2_flush(int device, int64_t bytes, wq8_stream_t stream);
+void wq8_l2_flush_release(void);
+
+/* ---- additions of this library (no counterpart in the reference) -------------------------------------- */
+
+/* Exact INT32 block dot products S[b][m][n] = sum over block b of a[m, k] * b[n, k], written to
+ * sums (ceil(K/128), M, N) int32 by the same tensor-core pipeline as wq8_gemm: the debug hook the parity
+ * tests use to check the INT32 sums bit for bit. */
+int wq8_debug_block_sums(const int8_t* a, const int8_t* b, int32_t* sums, int m, int n, int k, int sms, wq8_stream_t stream);
+
+/* Device-side status word of the GEMM pipeline on the current device: 0, or a code left by a bounded wait
+ * that gave up (the kernel then returned early with unspecified output).  Synchronizes the device; clears
+ * the word.  For tests and diagnostics only. */
+int wq8_debug_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WQ8_H */

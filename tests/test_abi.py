@@ -1,0 +1,99 @@
+"""The C-ABI library: it builds, loads without a GPU, exports every symbol include/wq8.h declares, identifies itself with the
+reference's ABI number, and rejects bad arguments with the reference's error codes before touching the device."""
+import ctypes
+import re
+import subprocess
+from pathlib import Path
+
+import pytest
+
+from wgpkernels_b200 import build as builder
+
+ROOT = Path(__file__).resolve().parents[1]
+p, i, i64, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+
+
+@pytest.fixture(scope="module")
+def lib():
+    handle = ctypes.CDLL(str(builder.build()))
+    handle.wq8_quantize.argtypes = [p, p, p, p, i, i, i64, i, i, i, p, f, p]
+    handle.wq8_quantize_blocks.argtypes = [p, p, p, i, i, i64, i, i, i, p, f, p, p]
+    handle.wq8_transform_rows.argtypes = [p, p, i, i, i64, i, i, i, p, f, p]
+    handle.wq8_rotate_groups.argtypes = [p, p, i, i, i64, i, i, p]
+    handle.wq8_gemm.argtypes = [p, p, p, p, p, p, p, p, p, i, i, i, i, i, i, i, p, p, p]
+    handle.wq8_gemm_workspace.argtypes = [i, i, i, i, i, i, p]
+    handle.wq8_gemm_workspace.restype = None
+    handle.wq8_small.argtypes = [p, i64, p, p, p, p, p, p, i, i, i, i, i, p, p, p]
+    handle.wq8_small_workspace.argtypes = [i, i, i, i, p]
+    handle.wq8_small_workspace.restype = None
+    handle.wq8_gemv_lines.argtypes = [p, i64, p, p, p, p, p, p, i, i, i, i, p]
+    return handle
+
+
+def declared_symbols():
+    text = "\n".join((ROOT / "include").glob("*.h").__next__().read_text().splitlines())
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(wq8_\w+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported():
+    library = builder.build()
+    listing = subprocess.run(["nm", "-D", "--defined-only", str(library)], capture_output=True, text=True, check=True).stdout
+    exported = {line.split()[-1] for line in listing.splitlines() if " T " in line}
+    declared = declared_symbols()
+    assert len(declared) >= 17
+    assert not [name for name in declared if name not in exported]
+    # nothing but the C ABI leaves the library (hidden visibility, static CUDA runtime)
+    assert all(name.startswith("wq8_") for name in exported), sorted(exported)[:10]
+
+
+def test_reference_entry_points_present(lib):
+    """The names the reference's ctypes table binds (wgpkernels/int8/__init__.py:73-89 of WGPKernels)."""
+    for name in ("wq8_abi", "wq8_features", "wq8_quantize", "wq8_quantize_blocks", "wq8_transform_rows", "wq8_l2_flush", "wq8_l2_flush_release",
+                 "wq8_gemm", "wq8_gemm_workspace", "wq8_gemm_select", "wq8_small", "wq8_small_workspace", "wq8_gemv_lines", "wq8_rotate_groups"):
+        assert hasattr(lib, name), name
+
+
+def test_identification(lib):
+    assert lib.wq8_abi() == 11
+    assert lib.wq8_features() & 1
+
+
+def test_empty_calls_return_zero(lib):
+    assert lib.wq8_quantize_blocks(None, None, None, 0, 256, 256, 1, 0, 0, None, 0.0, None, None) == 0
+    assert lib.wq8_quantize(None, None, None, None, 0, 256, 256, 1, 0, 0, None, 0.0, None) == 0
+    assert lib.wq8_transform_rows(None, None, 0, 256, 256, 1, 0, 0, None, 0.0, None) == 0
+    assert lib.wq8_gemm(None, None, None, None, None, None, None, None, None, 0, 96, 256, 1, 10, 148, 0, None, None, None) == 0
+    assert lib.wq8_small(None, 256, None, None, None, None, None, None, 0, 96, 256, 1, 148, None, None, None) == 0
+    assert lib.wq8_gemv_lines(None, 256, None, None, None, None, None, None, 0, 96, 256, 1, None) == 0
+
+
+def test_argument_errors(lib):
+    one = ctypes.c_void_p(16)  # never dereferenced: the checks come first
+    # a low part must accompany exactly the hi/lo variants
+    assert lib.wq8_gemm(one, None, one, one, one, None, None, None, one, 8, 96, 256, 1, 1, 148, 0, None, None, None) == -2
+    assert lib.wq8_gemm(one, one, one, one, one, None, None, None, one, 8, 96, 256, 1, 10, 148, 0, None, None, None) == -2
+    assert lib.wq8_gemm(one, None, one, one, one, None, None, None, one, 8, 96, 250, 1, 10, 148, 0, None, None, None) == -2  # K % 16
+    assert lib.wq8_gemm(one, None, one, one, one, None, None, None, one, 8, 96, 256, 2, 10, 148, 0, None, None, None) == -1  # fp32 output
+    assert lib.wq8_gemm(one, None, one, one, one, None, None, None, one, 8, 96, 256, 1, 99, 148, 0, None, None, None) == -3  # variant
+    assert lib.wq8_small(one, 256, one, one, None, None, None, one, 33, 96, 256, 1, 148, None, None, None) == -2
+    assert lib.wq8_small(one, 256, one, one, None, None, None, one, 8, 96, 200, 1, 148, None, None, None) == -2
+    assert lib.wq8_gemv_lines(one, 256, one, one, None, None, None, one, 5, 96, 256, 1, None) == -2
+    assert lib.wq8_gemv_lines(one, 256, one, one, None, None, None, one, 2, 96, 254, 1, None) == -2
+    assert lib.wq8_quantize_blocks(one, one, one, 4, 256, 256, 1, 32, 0, None, 0.0, None, None) == -1  # group
+    assert lib.wq8_quantize_blocks(one, one, one, 4, 256, 256, 1, 0, 7, None, 0.0, None, None) == -1   # act
+    assert lib.wq8_quantize_blocks(one, one, one, 4, 256, 256, 2, 0, 1, None, 0.0, None, None) == -1   # fp32 input takes no op
+    assert lib.wq8_quantize(one, one, None, one, 4, 256, 256, 5, 0, 0, None, 0.0, None) == -1          # dtype
+    assert lib.wq8_rotate_groups(one, one, 4, 256, 256, 1, 0, None) == -1
+
+
+def test_workspace_queries(lib):
+    sizes = (ctypes.c_int64 * 2)()
+    lib.wq8_gemm_workspace(32760, 15360, 5120, 10, 148, 1, sizes)
+    assert sizes[0] >= 0 and sizes[1] >= 0 and sizes[1] <= 4096
+    # few tokens, few channels: K is split across CTAs and the partial sums need slots and one counter per tile
+    lib.wq8_small_workspace(16, 1024, 14336, 148, sizes)
+    assert sizes[0] > 0 and 0 < sizes[1] <= 4096
+    # many channels: every SM streams without splitting
+    lib.wq8_small_workspace(16, 28672, 4096, 148, sizes)
+    assert sizes[0] == 0 and sizes[1] == 0

@@ -1,0 +1,158 @@
+"""The tcgen05 INT8 GEMM on the GPU: exact INT32 block sums, every mode against the CPU oracle and against the reference's own CUDA
+library, tails, in-place residual, determinism, and row / column partition invariance at full size."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import int8_oracle as oracle
+from tests import reflib
+from tests.gpu_common import rand_int8, randn, rel
+from wgpkernels_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+
+MODES = {"row": 0, "exact": 1, "block": 10, "block-cvt": 11, "block+g": 12, "block+g-cvt": 13, "exact+g": 14}
+REF_VARIANT = {"row": 2, "exact": 1, "block": 10, "block-cvt": 10, "block+g": 12, "block+g-cvt": 12, "exact+g": 14}
+
+
+def operands(mode, m, n, k, dtype, seed, residual=False):
+    """Random INT8 operands with the scale layout of `mode`, on the CPU."""
+    base = mode.removesuffix("-cvt")
+    kb = -(-k // 128)
+    g = torch.Generator().manual_seed(seed)
+    a = rand_int8((m, k), seed)
+    a_lo = rand_int8((m, k), seed + 1) if base.startswith("exact") else None
+    sa = torch.rand((m, kb) if base.startswith("block") else (m,), generator=g) * 0.02 + 0.001
+    b = rand_int8((n, k), seed + 2)
+    sb = torch.rand((n, kb) if base.endswith("+g") else (n,), generator=g) * 0.01 + 0.0005
+    bias = randn((n,), dtype, seed + 3)
+    res = randn((m, n), dtype, seed + 4, 4.0) if residual else None
+    rs = torch.rand(n, generator=g).to(dtype) if residual else None
+    return base, a, a_lo, sa, b, sb, bias, res, rs
+
+
+def run(wq, mode, a, a_lo, sa, b, sb, bias, res, rs, dtype, out=None):
+    dev = lambda t: None if t is None else t.cuda()
+    return wq.gemm(dev(a), dev(a_lo), dev(sa), dev(b), dev(sb), dev(bias), dtype, 0, MODES[mode], out=out, residual=dev(res) if out is None else out,
+                   residual_scale=dev(rs))
+
+
+@pytest.mark.parametrize("shape", [(40, 96, 256), (128, 256, 128), (129, 257 * 8, 384), (300, 520, 1024 + 16), (1, 8, 16)], ids=str)
+def test_block_sums_are_exact(wq, shape):
+    """The INT32 sums the tensor cores leave in tensor memory, per 128-element block of K, bit for bit."""
+    m, n, k = shape
+    a, b = rand_int8((m, k), 1), rand_int8((n, k), 2)
+    sums = wq.debug_block_sums(a.cuda(), b.cuda())
+    assert wq.debug_status() == 0
+    assert np.array_equal(sums.cpu().numpy(), oracle.block_sums(a.numpy(), b.numpy()))
+
+
+def test_block_sums_extreme_values(wq):
+    """All operands at +-127: the largest block sums (128 * 127 * 127) the conversion must hold."""
+    m, n, k = 128, 256, 512
+    a = torch.full((m, k), 127, dtype=torch.int8)
+    b = torch.full((n, k), -127, dtype=torch.int8)
+    b[::2] = 127
+    sums = wq.debug_block_sums(a.cuda(), b.cuda())
+    assert np.array_equal(sums.cpu().numpy(), oracle.block_sums(a.numpy(), b.numpy()))
+    sa, sb = torch.ones(m, 4), torch.ones(n)
+    y = wq.gemm(a.cuda(), None, sa.cuda(), b.cuda(), sb.cuda(), None, torch.bfloat16, 0, 10)
+    y2 = wq.gemm(a.cuda(), None, sa.cuda(), b.cuda(), sb.cuda(), None, torch.bfloat16, 0, 11)
+    expected = oracle.gemm("block", a.numpy(), None, sa.numpy(), b.numpy(), sb.numpy())
+    assert torch.equal(y.cpu(), expected) and torch.equal(y2.cpu(), expected)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+@pytest.mark.parametrize("residual", [False, True], ids=["plain", "residual"])
+@pytest.mark.parametrize("mode", list(MODES))
+@pytest.mark.parametrize("shape", [(40, 96, 256), (130, 264, 640), (257, 520, 1024 + 48)], ids=str)
+def test_modes_match_oracle(wq, shape, mode, residual, dtype):
+    m, n, k = shape
+    base, a, a_lo, sa, b, sb, bias, res, rs = operands(mode, m, n, k, dtype, 31, residual)
+    y = run(wq, mode, a, a_lo, sa, b, sb, bias, res, rs, dtype)
+    assert wq.debug_status() == 0
+    expected = oracle.gemm(base, a.numpy(), None if a_lo is None else a_lo.numpy(), sa.numpy(), b.numpy(), sb.numpy(), bias, res, rs, dtype)
+    # same FP32 operation order as the oracle: identical up to the rare double rounding of the oracle's emulated FMA
+    mismatch = (y.cpu() != expected).float().mean().item()
+    assert mismatch < 1e-3, mismatch
+    assert rel(y, expected) < 2e-5
+
+
+@pytest.mark.parametrize("mode", list(MODES))
+def test_modes_match_reference_library(wq, mode):
+    m, n, k = 1000, 1536, 2048
+    dtype = torch.bfloat16
+    base, a, a_lo, sa, b, sb, bias, res, rs = operands(mode, m, n, k, dtype, 41, True)
+    y = run(wq, mode, a, a_lo, sa, b, sb, bias, res, rs, dtype)
+    dev = lambda t: None if t is None else t.cuda()
+    y_ref = reflib.gemm(dev(a), dev(a_lo), dev(sa), dev(b), dev(sb), dev(bias), dtype, REF_VARIANT[mode], 0, dev(res), dev(rs))
+    assert rel(y, y_ref) < 1e-3
+    assert (y != y_ref).float().mean().item() < 1e-3
+
+
+def test_odd_output_width(wq):
+    """N not a multiple of 8: element-wise stores."""
+    m, n, k = 70, 100 + 3, 256
+    base, a, a_lo, sa, b, sb, bias, res, rs = operands("block", m, n, k, torch.bfloat16, 51, True)
+    y = run(wq, "block", a, a_lo, sa, b, sb, bias, res, rs, torch.bfloat16)
+    expected = oracle.gemm("block", a.numpy(), None, sa.numpy(), b.numpy(), sb.numpy(), bias, res, rs, torch.bfloat16)
+    assert rel(y, expected) < 2e-5
+
+
+def test_in_place_residual_and_determinism(wq):
+    m, n, k = 300, 768, 1024
+    base, a, a_lo, sa, b, sb, bias, res, rs = operands("block", m, n, k, torch.bfloat16, 61, True)
+    y = run(wq, "block", a, a_lo, sa, b, sb, bias, res, rs, torch.bfloat16)
+    target = res.cuda().clone()
+    y2 = run(wq, "block", a, a_lo, sa, b, sb, bias, res, rs, torch.bfloat16, out=target)
+    assert y2.data_ptr() == target.data_ptr()
+    assert torch.equal(y, y2)
+    assert torch.equal(y, run(wq, "block", a, a_lo, sa, b, sb, bias, res, rs, torch.bfloat16))
+
+
+def test_weight_row_ranges(wq):
+    """A row range of the weight (and of its scales and bias) computes the matching output columns, bit for bit."""
+    m, n, k = 200, 1024, 512
+    base, a, a_lo, sa, b, sb, bias, res, rs = operands("block", m, n, k, torch.bfloat16, 71)
+    a, sa, b, sb, bias = a.cuda(), sa.cuda(), b.cuda(), sb.cuda(), bias.cuda()
+    full = wq.gemm(a, None, sa, b, sb, bias, torch.bfloat16, 0, 10)
+    part = wq.gemm(a, None, sa, b[256:640], sb[256:640], bias[256:640], torch.bfloat16, 0, 10)
+    assert torch.equal(full[:, 256:640], part)
+    rows = wq.gemm(a[64:150], None, sa[64:150], b, sb, bias, torch.bfloat16, 0, 10)
+    assert torch.equal(full[64:150], rows)
+
+
+@pytest.mark.parametrize("name", ["c1", "c2"])
+def test_full_size_rows_against_oracle(wq, name):
+    """BASELINE configs 1 and 2 at full width (N, K) on a band of rows that spans tile boundaries, through linear():
+    the INT8 codes and scales feed the oracle's GEMM, so only the FP32 accumulation order of the GEMM is compared."""
+    c = workloads.make(name, rows=300)
+    g = c.to("cuda")
+    y = wq.linear(g.x, g.weight, g.scale, g.bias, mode="block", act=c.act, act_weight=g.act_weight, eps=c.eps, residual=g.residual,
+                  residual_scale=g.residual_scale)
+    assert wq.debug_status() == 0
+    q, sa = wq.quantize_blocks(g.x, 0, c.act, g.act_weight, c.eps)
+    expected = oracle.gemm("block", q.cpu().numpy(), None, sa.cpu().numpy(), c.weight.numpy(), c.scale.numpy(), c.bias, c.residual, c.residual_scale,
+                           torch.bfloat16)
+    assert (y.cpu() != expected).float().mean().item() < 1e-3
+    assert rel(y, expected) < 2e-5
+    reference = oracle.linear_reference(c.x, c.weight, c.scale, c.bias, 0, c.act, c.act_weight, c.eps, c.residual, c.residual_scale)
+    assert rel(y, reference) < 3e-2  # the block path's own quantization error against FP32, the reference's selftest bar
+
+
+def test_full_size_partition_invariance(wq):
+    """BASELINE config 1 at full size (M = 32760): every output element is computed by the same instruction sequence wherever its
+    tile lies, so row bands and column bands of the problem reproduce the full result bit for bit; the band results are themselves
+    checked against the oracle by the test above."""
+    c = workloads.make("c1").to("cuda")
+    prepared = wq.prepare(c.x, 0, "block", c.act, c.act_weight, c.eps)
+    full = wq.linear_prepared(prepared, c.weight, c.scale, c.bias)
+    assert wq.debug_status() == 0
+    band = wq.linear_prepared(prepared.rows(12345, 12345 + 700), c.weight, c.scale, c.bias)
+    assert torch.equal(full[12345:12345 + 700], band)
+    cols = wq.linear_prepared(prepared, c.weight[7680:9216], c.scale[7680:9216], None)
+    assert torch.equal(full[:, 7680:9216], cols)
+    checksum = full.float().sum(dim=0)
+    assert torch.isfinite(checksum).all()
+    again = wq.linear_prepared(prepared, c.weight, c.scale, c.bias)
+    assert torch.equal(full, again)

@@ -1,0 +1,75 @@
+"""Few-token weight-streaming kernels ('lines', 'small') on the GPU against the CPU oracle and the reference's own CUDA library."""
+import pytest
+import torch
+
+from oracle import int8_oracle as oracle
+from tests import reflib
+from tests.gpu_common import rand_int8, randn, rel
+
+pytestmark = pytest.mark.gpu
+
+
+def case(m, n, k, dtype, seed, residual):
+    g = torch.Generator().manual_seed(seed)
+    x = randn((m, k), dtype, seed)
+    x[:, :4] = 1000.0 if dtype == torch.bfloat16 else 100.0  # massive-activation channels
+    w = rand_int8((n, k), seed + 1)
+    sw = torch.rand(n, generator=g) * 0.002 + 0.0001
+    bias = randn((n,), dtype, seed + 2)
+    res = randn((m, n), dtype, seed + 3, 4.0) if residual else None
+    rs = torch.rand(n, generator=g).to(dtype) if residual else None
+    return x, w, sw, bias, res, rs
+
+
+def cuda(*tensors):
+    return [None if t is None else t.cuda() for t in tensors]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+@pytest.mark.parametrize("residual", [False, True], ids=["plain", "residual"])
+@pytest.mark.parametrize("shape", [(1, 96, 256), (2, 100, 260), (3, 4096, 1024), (4, 520, 4096 + 64), (4, 28672, 4096), (1, 4096, 14336)], ids=str)
+def test_lines(wq, shape, residual, dtype):
+    m, n, k = shape
+    x, w, sw, bias, res, rs = case(m, n, k, dtype, 101, residual)
+    gx, gw, gsw, gbias, gres, grs = cuda(x, w, sw, bias, res, rs)
+    y = wq.gemv_lines(gx, gw, gsw, gbias, gres, grs)
+    expected = oracle.weight_only(x, w.numpy(), sw.numpy(), bias, res, rs, dtype)
+    assert rel(y, expected) < 1e-3
+    y_ref = reflib.gemv_lines(gx, gw, gsw, gbias, gres, grs)
+    assert rel(y, y_ref) < 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+@pytest.mark.parametrize("residual", [False, True], ids=["plain", "residual"])
+@pytest.mark.parametrize("shape", [(5, 96, 256), (8, 1000, 1024), (16, 28672, 4096), (16, 4096, 14336), (32, 4096, 14336), (32, 1024, 8192), (9, 40, 64),
+                                   (24, 2048, 4096)], ids=str)
+def test_small(wq, shape, residual, dtype):
+    m, n, k = shape
+    x, w, sw, bias, res, rs = case(m, n, k, dtype, 111, residual)
+    gx, gw, gsw, gbias, gres, grs = cuda(x, w, sw, bias, res, rs)
+    y = wq.small(gx, gw, gsw, gbias, gres, grs)
+    expected = oracle.weight_only(x, w.numpy(), sw.numpy(), bias, res, rs, dtype)
+    assert rel(y, expected) < 1e-3
+    y_ref = reflib.small(gx, gw, gsw, gbias, gres, grs)
+    assert rel(y, y_ref) < 1e-3
+    assert torch.equal(y, wq.small(gx, gw, gsw, gbias, gres, grs))  # fixed-order reductions: run to run identical
+    # the split-K counters are left zeroed
+    assert not wq._counters[0].any().item()
+
+
+def test_small_in_place_residual(wq):
+    x, w, sw, bias, res, rs = case(12, 1024, 2048, torch.bfloat16, 121, True)
+    gx, gw, gsw, gbias, gres, grs = cuda(x, w, sw, bias, res, rs)
+    y = wq.small(gx, gw, gsw, gbias, gres, grs)
+    target = gres.clone()
+    wq.small(gx, gw, gsw, gbias, target, grs, out=target)
+    assert torch.equal(y, target)
+
+
+def test_strided_activation(wq):
+    wide = randn((4, 4096), torch.bfloat16, 131).cuda()
+    x = wide[:, 1024:3072]
+    w = rand_int8((256, 2048), 132).cuda()
+    sw = torch.full((256,), 0.001).cuda()
+    assert torch.equal(wq.gemv_lines(x, w, sw), wq.gemv_lines(x.contiguous(), w, sw))
+    assert torch.equal(wq.small(x, w, sw), wq.small(x.contiguous(), w, sw))

@@ -1,0 +1,614 @@
+// INT8 x INT8 -> INT32 GEMM on the 5th-generation tensor cores of sm_100a (tcgen05.mma kind::i8, accumulators in tensor memory),
+// operands staged by TMA (no cluster multicast: every CTA loads its own tiles from its GPU's own memory), warp-specialised:
+//
+//   warp 0      TMA producer: A (and A_lo) 128 x 128-byte tiles, B BN x 128-byte tiles, 128-byte swizzle, ring of STAGES buffers
+//   warp 1      MMA issuer: one elected thread, 4 (x2 with a low part) tcgen05.mma of K = 32 per stage
+//   warps 2-3   tensor-memory allocation; gather of per-(n, k-block) weight scales into a shared-memory ring (group-scaled weights)
+//   warps 4-11  epilogue: tcgen05.ld of the INT32 sums, promotion to FP32, bias / residual, one rounding, stores
+//
+// Modes (the arithmetic of wgpkernels/int8/int8_gemm.cu:773-805 and :836-863 of WGPKernels):
+//   row      INT32 sums over all K; y = fmaf(float(S) * sa[m], sb[n], bias)
+//   exact    hi and lo operands share B; v = fmaf(float(S_lo), 1/254, float(S_hi)); y = fmaf(v * sa[m], sb[n], bias)
+//   block    per 128 of K: acc = fmaf(float(S_b), sa[m, b], acc); y = fmaf(acc, sb[n], bias)
+//   block+g  acc = fmaf(float(S_b), sa[m, b] * sb[n, b], acc); y = acc + bias
+//   exact+g  acc = fmaf(fmaf(float(S_lo_b), 1/254, float(S_hi_b)), sb[n, b], acc); y = fmaf(acc * sa[m], 1, bias)
+// then y = fmaf(y, rscale[n], residual[m, n]) and one rounding.  In the per-block modes the tensor cores produce one exact INT32 block
+// sum per output and 128 of K into a double-buffered tensor-memory accumulator; the epilogue warps drain a buffer (128 x 256 sums) while
+// the MMAs of the next block fill the other one, and keep the FP32 accumulators in registers for the whole tile.
+//
+// Every wait is bounded: a wait that gives up records a code in a device status word, raises a CTA-wide abort flag and the CTA leaves
+// through the common exit (tensor memory is always released).
+#include <cuda.h>  // CUtensorMap and its enums only; cuTensorMapEncodeTiled is resolved through the runtime, libcuda is not linked
+
+#include "common.cuh"
+
+namespace wq {
+
+enum Mode : int { kRow = 0, kExact = 1, kBlock = 2, kBlockG = 3, kExactG = 4 };
+
+constexpr int kBM = 128;             // rows of a tile = tensor-memory lanes
+constexpr int kStageK = 128;         // bytes (= INT8 elements) of K per stage: one 128-byte swizzle row, one scale block
+constexpr int kMmaK = 32;            // K of one tcgen05.mma kind::i8
+constexpr int kTmemColumns = 512;    // all of an SM's tensor memory (one CTA per SM)
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 32 * (4 + kEpilogueWarps);
+constexpr int kScaleRing = 4;        // blocks of gathered weight scales in flight
+constexpr long long kWaitLimit = 4000000000ll;  // clocks (about two seconds) before a wait gives up
+
+__device__ int g_status = 0;  // first code of a wait that gave up (wq::Status)
+
+// ---- PTX wrappers --------------------------------------------------------------------------------------------------
+WQ_DEVICE uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+WQ_DEVICE void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
+WQ_DEVICE void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+WQ_DEVICE void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+WQ_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Waits for the phase of `parity`; false when the CTA is aborting or the wait ran out (then `code` is recorded and the abort flag raised).
+WQ_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 15u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - start > kWaitLimit) {
+                *abort_flag = code;
+                atomicCAS(&g_status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+WQ_DEVICE void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst), "l"(map),
+                 "r"(bar), "r"(x), "r"(y)
+                 : "memory");
+}
+WQ_DEVICE void prefetch_tensormap(const CUtensorMap* map) { asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory"); }
+
+WQ_DEVICE void tmem_alloc(uint32_t slot_in_smem, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_in_smem), "r"(columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+WQ_DEVICE void tmem_dealloc(uint32_t address, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+WQ_DEVICE void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+WQ_DEVICE void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// The mbarrier is arrived on once every tcgen05 operation this thread issued before has completed.
+WQ_DEVICE void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D (tensor memory, 128 lanes x N columns of INT32) = or += A (128 x 32 INT8, smem) * B (N x 32 INT8, smem)^T
+WQ_DEVICE void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// 32 consecutive columns of this thread's lane (a warp reads the 32 lanes of its quarter of tensor memory).
+#define WQ_R4(a, i) "=r"(a[i]), "=r"(a[i + 1]), "=r"(a[i + 2]), "=r"(a[i + 3])
+WQ_DEVICE void tmem_load_32(uint32_t taddr, int* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : WQ_R4(v, 0), WQ_R4(v, 4), WQ_R4(v, 8), WQ_R4(v, 12), WQ_R4(v, 16), WQ_R4(v, 20), WQ_R4(v, 24), WQ_R4(v, 28)
+        : "r"(taddr)
+        : "memory");
+}
+#undef WQ_R4
+// Completes the loads above.  The registers are operands so that no use of them can be scheduled before the wait.
+#define WQ_RW4(a, i) "+r"(a[i]), "+r"(a[i + 1]), "+r"(a[i + 2]), "+r"(a[i + 3])
+WQ_DEVICE void tmem_load_wait(int* v) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : WQ_RW4(v, 0), WQ_RW4(v, 4), WQ_RW4(v, 8), WQ_RW4(v, 12), WQ_RW4(v, 16), WQ_RW4(v, 20), WQ_RW4(v, 24), WQ_RW4(v, 28)
+                 :
+                 : "memory");
+}
+#undef WQ_RW4
+
+// Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+WQ_DEVICE uint64_t smem_descriptor(uint32_t address) {
+    uint64_t d = (address & 0x3ffffu) >> 4;       // start address, 16-byte units
+    d |= uint64_t(1) << 16;                       // leading byte offset (unused for swizzled K-major layouts)
+    d |= uint64_t(1024 >> 4) << 32;               // stride byte offset between 8-row groups
+    d |= uint64_t(1) << 46;                       // descriptor version of sm_100
+    d |= uint64_t(2) << 61;                       // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: INT32 accumulator, signed INT8 A and B, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t instruction_descriptor(int n) { return (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(kBM >> 4) << 24); }
+
+// Exact INT32 -> FP32 of a block sum.  |sum| <= 128 * 127 * 127 < 2^22, so adding it to the bits of 1.5 * 2^23 gives the float
+// 1.5 * 2^23 + sum exactly and one subtraction recovers it; CVT selects the conversion instruction instead.
+template <int CVT> WQ_DEVICE float block_sum_to_float(int s) {
+    if constexpr (CVT) return __int2float_rn(s);
+    return __int_as_float(s + 0x4B400000) - 12582912.f;
+}
+
+template <int MODE, int BN> struct Shape {
+    static constexpr bool kHilo = MODE == kExact || MODE == kExactG;
+    static constexpr bool kFold = MODE == kBlock || MODE == kBlockG || MODE == kExactG;  // one accumulation per 128 of K
+    static constexpr bool kWGroup = MODE == kBlockG || MODE == kExactG;
+    static constexpr bool kBlockScales = MODE == kBlock || MODE == kBlockG;              // sa is (M, ceil(K / 128))
+    static constexpr int kAccColumns = BN * (kHilo ? 2 : 1);
+    static constexpr int kAccBuffers = kTmemColumns / kAccColumns;
+    static constexpr int kABytes = kBM * kStageK, kBBytes = BN * kStageK;
+    static constexpr int kStageBytes = kABytes * (kHilo ? 2 : 1) + kBBytes;
+    static constexpr int kStages = (196 * 1024) / kStageBytes;
+    static constexpr int kEpiColumns = BN / 2;  // columns per epilogue thread (two warpgroups split the tile's columns)
+    static constexpr int kRingBytes = kWGroup ? kScaleRing * BN * 4 : 0;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kRingBytes + 1024 /* alignment */ + 256 /* barriers */;
+    static_assert(kAccBuffers >= 1 && kStages >= 2, "tile does not fit");
+};
+
+struct GemmParams {
+    const float* sa;
+    const float* sb;
+    const void* bias;
+    const void* residual;
+    const void* rscale;
+    void* y;
+    int* dump;  // debug: raw block sums (kblocks, M, N)
+    int m, n, k;
+    int tiles_m, tiles_n;
+    int vector_io;  // y / residual rows allow 16-byte accesses
+};
+
+struct TileCoord { int m0, n0; };
+// Bands of 16 row tiles are swept over all column tiles, so the CTAs running together share a few A bands and B tiles in L2.
+template <int BN> WQ_DEVICE TileCoord tile_origin(int t, int tiles_m, int tiles_n) {
+    constexpr int kBand = 16;
+    const int width = kBand * tiles_n, first = (t / width) * kBand;
+    const int rows = min(tiles_m - first, kBand);
+    return {(first + (t % width) % rows) * kBM, ((t % width) / rows) * BN};
+}
+
+template <class T, int MODE, int BN, int CVT, bool DUMP>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b,
+           const GemmParams p) {
+    using S = Shape<MODE, BN>;
+    constexpr int kStages = S::kStages, kAccBuffers = S::kAccBuffers, kEpi = S::kEpiColumns;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float* scale_ring = reinterpret_cast<float*>(smem + kStages * S::kStageBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes + S::kRingBytes);
+    // barrier layout: full[kStages], empty[kStages], acc_full[2], acc_empty[2], ring_full[kScaleRing], ring_empty[kScaleRing]
+    const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * kStages, bar_acc_full = bar_empty + 8 * kStages,
+                   bar_acc_empty = bar_acc_full + 16, bar_ring_full = bar_acc_empty + 16, bar_ring_empty = bar_ring_full + 8 * kScaleRing;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_word;
+    volatile int* abort_flag = &abort_word;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kblocks = (p.k + kStageK - 1) / kStageK;
+    const int tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        abort_word = 0;
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar_acc_full + 8 * s, 1);
+            mbar_init(bar_acc_empty + 8 * s, kEpilogueWarps);
+        }
+        for (int s = 0; s < kScaleRing; ++s) {
+            mbar_init(bar_ring_full + 8 * s, 64);
+            mbar_init(bar_ring_empty + 8 * s, kEpilogueWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        if (S::kHilo) prefetch_tensormap(&map_a_lo);
+    }
+    if (warp == 2) tmem_alloc(smem_u32(&tmem_slot), kTmemColumns);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    // Registers move from the four control warps to the eight epilogue warps, which hold a tile's FP32 accumulators:
+    // 128 x 56 + 256 x 224 = 64512 registers, what 384 threads x 168 were launched with.
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+                const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n);
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kTimeoutEmpty))) break;
+                    const uint32_t full = bar_full + 8 * stage;
+                    const uint32_t dst = smem_u32(smem + stage * S::kStageBytes);
+                    mbar_expect_tx(full, S::kStageBytes);
+                    tma_load_2d(dst, &map_a, full, kb * kStageK, c.m0);
+                    if (S::kHilo) tma_load_2d(dst + S::kABytes, &map_a_lo, full, kb * kStageK, c.m0);
+                    tma_load_2d(dst + S::kABytes * (S::kHilo ? 2 : 1), &map_b, full, kb * kStageK, c.n0);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // aborting: let the copies already issued land before the CTA's shared memory is given back
+                for (int s = 0; s < kStages; ++s) {
+                    const long long start = clock64();
+                    while (!mbar_try_wait(bar_full + 8 * s, 0) && !mbar_try_wait(bar_full + 8 * s, 1) && clock64() - start < 2000000) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = instruction_descriptor(BN);
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    const bool new_acc = S::kFold || kb == 0;
+                    if (new_acc && !(ok = mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kTimeoutTmemEmpty))) break;
+                    if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, kTimeoutFull))) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + stage * S::kStageBytes);
+                    const uint64_t a_desc = smem_descriptor(a_addr), a_lo_desc = smem_descriptor(a_addr + S::kABytes),
+                                   b_desc = smem_descriptor(a_addr + S::kABytes * (S::kHilo ? 2 : 1));
+                    const uint32_t d = tmem_base + acc * S::kAccColumns;
+#pragma unroll
+                    for (int j = 0; j < kStageK / kMmaK; ++j) {
+                        const uint32_t accumulate = (new_acc && j == 0) ? 0u : 1u;
+                        const uint64_t step = uint64_t(j * kMmaK >> 4);  // start address advances in 16-byte units inside the swizzle row
+                        mma_i8(d, a_desc + step, b_desc + step, idesc, accumulate);
+                        if (S::kHilo) mma_i8(d + BN, a_lo_desc + step, b_desc + step, idesc, accumulate);
+                    }
+                    tc_commit(bar_empty + 8 * stage);  // the stage may be refilled once these MMAs have read it
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    if (S::kFold || kb == kblocks - 1) {
+                        tc_commit(bar_acc_full + 8 * acc);
+                        if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1u; }
+                    }
+                }
+            }
+        }
+    } else if (warp < 4) {
+        // ---------------- weight-scale gather (group-scaled weights) ----------------
+        if constexpr (S::kWGroup) {
+            const int loader = threadIdx.x - 64;  // 0..63
+            int slot = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+                const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n);
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!(ok = mbar_wait(bar_ring_empty + 8 * slot, phase ^ 1u, abort_flag, kTimeoutScales))) break;
+                    for (int i = loader; i < BN; i += 64) {
+                        const int col = c.n0 + i;
+                        scale_ring[slot * BN + i] = col < p.n ? __ldg(p.sb + int64_t(col) * kblocks + kb) : 0.f;
+                    }
+                    mbar_arrive(bar_ring_full + 8 * slot);
+                    if (++slot == kScaleRing) { slot = 0; phase ^= 1u; }
+                }
+            }
+        }
+    }
+    } else {
+        // ---------------- epilogue ----------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        const int quarter = warp & 3, half = (warp - 4) >> 2;
+        const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+        const T* bias = static_cast<const T*>(p.bias);
+        const T* residual = static_cast<const T*>(p.residual);
+        const T* rscale = static_cast<const T*>(p.rscale);
+        T* y = static_cast<T*>(p.y);
+        int acc = 0, slot = 0;
+        uint32_t acc_phase = 0, ring_phase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+            const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n);
+            const int row = c.m0 + quarter * 32 + lane;
+            const bool row_ok = row < p.m;
+            const int col0 = c.n0 + half * kEpi;
+            const float row_scale = S::kBlockScales ? 1.f : (row_ok ? __ldg(p.sa + row) : 0.f);
+
+            // y values of 32 columns starting at `col`: bias, residual, one rounding, store
+            auto emit = [&](const float* v, int col) {
+                if (!row_ok || col >= p.n) return;
+                float out[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int cj = col + j;
+                    const bool in = cj < p.n;
+                    const float col_scale = S::kWGroup ? 1.f : (in ? __ldg(p.sb + cj) : 0.f);
+                    const float b = bias && in ? as_float(bias[cj]) : 0.f;
+                    out[j] = fmaf(v[j] * row_scale, col_scale, b);
+                }
+                T* dst = y + int64_t(row) * p.n + col;
+                const T* res = residual ? residual + int64_t(row) * p.n + col : nullptr;
+                if (p.vector_io) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        if (col + j >= p.n) break;
+                        if (res) {
+                            const uint4 raw = *reinterpret_cast<const uint4*>(res + j);
+                            const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                float r0, r1;
+                                unpack_pair<T>(words[e], r0, r1);
+                                const int cj = col + j + 2 * e;
+                                out[j + 2 * e] = fmaf(out[j + 2 * e], rscale ? as_float(rscale[cj]) : 1.f, r0);
+                                out[j + 2 * e + 1] = fmaf(out[j + 2 * e + 1], rscale ? as_float(rscale[cj + 1]) : 1.f, r1);
+                            }
+                        }
+                        uint4 packed;
+                        packed.x = pack_pair<T>(out[j], out[j + 1]);
+                        packed.y = pack_pair<T>(out[j + 2], out[j + 3]);
+                        packed.z = pack_pair<T>(out[j + 4], out[j + 5]);
+                        packed.w = pack_pair<T>(out[j + 6], out[j + 7]);
+                        *reinterpret_cast<uint4*>(dst + j) = packed;
+                    }
+                } else {
+                    for (int j = 0; j < 32 && col + j < p.n; ++j) {
+                        float v1 = out[j];
+                        if (res) v1 = fmaf(v1, rscale ? as_float(rscale[col + j]) : 1.f, as_float(res[j]));
+                        dst[j] = round_one<T>(v1);
+                    }
+                }
+            };
+
+            if constexpr (S::kFold) {
+                float accf[kEpi];
+#pragma unroll
+                for (int j = 0; j < kEpi; ++j) accf[j] = 0.f;
+                // activation block scales: two blocks ahead in registers
+                float sa_now = 0.f, sa_next = 0.f;
+                if constexpr (S::kBlockScales && !DUMP) {
+                    const float* sa_row = p.sa + int64_t(row_ok ? row : 0) * kblocks;
+                    sa_now = row_ok ? __ldg(sa_row) : 0.f;
+                    sa_next = row_ok && kblocks > 1 ? __ldg(sa_row + 1) : 0.f;
+                }
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    float sa_after = 0.f;
+                    if constexpr (S::kBlockScales && !DUMP) {
+                        if (row_ok && kb + 2 < kblocks) sa_after = __ldg(p.sa + int64_t(row) * kblocks + kb + 2);
+                    }
+                    if constexpr (S::kWGroup) {
+                        if (!(ok = __all_sync(0xffffffffu, mbar_wait(bar_ring_full + 8 * slot, ring_phase, abort_flag, kTimeoutScales)))) break;
+                    }
+                    if (!(ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, kTimeoutTmemFull)))) break;
+                    tc_fence_after();
+                    const uint32_t taddr = tmem_base + lane_base + acc * S::kAccColumns + half * kEpi;
+                    const float* ring = scale_ring + slot * BN + half * kEpi;
+#pragma unroll
+                    for (int chunk = 0; chunk < kEpi / 32; ++chunk) {
+                        int s_hi[32], s_lo[32];
+                        tmem_load_32(taddr + chunk * 32, s_hi);
+                        if (S::kHilo) tmem_load_32(taddr + BN + chunk * 32, s_lo);
+                        tmem_load_wait(s_hi);
+                        if (S::kHilo) tmem_load_wait(s_lo);
+                        if constexpr (DUMP) {
+                            if (row_ok)
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    if (col0 + chunk * 32 + j < p.n) p.dump[(int64_t(kb) * p.m + row) * p.n + col0 + chunk * 32 + j] = s_hi[j];
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            float* a = &accf[chunk * 32 + j];
+                            if constexpr (MODE == kBlock) {
+                                *a = fmaf(block_sum_to_float<CVT>(s_hi[j]), sa_now, *a);
+                            } else if constexpr (MODE == kBlockG) {
+                                *a = fmaf(block_sum_to_float<CVT>(s_hi[j]), sa_now * ring[chunk * 32 + j], *a);
+                            } else {
+                                const float v = fmaf(block_sum_to_float<CVT>(s_lo[j]), 1.f / 254.f, block_sum_to_float<CVT>(s_hi[j]));
+                                *a = fmaf(v, ring[chunk * 32 + j], *a);
+                            }
+                        }
+                    }
+                    // this warp is done with the accumulator buffer (and the scale slot): hand them back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(bar_acc_empty + 8 * acc);
+                        if (S::kWGroup) mbar_arrive(bar_ring_empty + 8 * slot);
+                    }
+                    if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1u; }
+                    if (S::kWGroup && ++slot == kScaleRing) { slot = 0; ring_phase ^= 1u; }
+                    sa_now = sa_next;
+                    sa_next = sa_after;
+                }
+                if (!ok) break;
+                if constexpr (!DUMP) {
+#pragma unroll
+                    for (int chunk = 0; chunk < kEpi / 32; ++chunk) emit(&accf[chunk * 32], col0 + chunk * 32);
+                }
+            } else {
+                if (!(ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, kTimeoutTmemFull)))) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + lane_base + acc * S::kAccColumns + half * kEpi;
+#pragma unroll 1
+                for (int chunk = 0; chunk < kEpi / 32; ++chunk) {
+                    int s_hi[32], s_lo[32];
+                    tmem_load_32(taddr + chunk * 32, s_hi);
+                    if (S::kHilo) tmem_load_32(taddr + BN + chunk * 32, s_lo);
+                    tmem_load_wait(s_hi);
+                    if (S::kHilo) tmem_load_wait(s_lo);
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        v[j] = float(s_hi[j]);
+                        if (S::kHilo) v[j] = fmaf(float(s_lo[j]), 1.f / 254.f, v[j]);
+                    }
+                    if (chunk == kEpi / 32 - 1) {
+                        // all of this warp's columns are in registers: the MMAs of the next tile may overwrite the buffer
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+                    }
+                    emit(v, col0 + chunk * 32);
+                }
+                if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+    }
+
+    // common exit: every role falls through to here, aborting or not
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------------------------------------
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) == cudaSuccess && result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(p);
+    }
+    return fn;
+}
+
+// (rows, k) row-major INT8 matrix -> tensor map with boxes of `box_rows` rows x 128 bytes, 128-byte swizzle, zero fill outside.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(k)};
+    const cuuint32_t box[2] = {cuuint32_t(kStageK), cuuint32_t(box_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct GemmArgs {
+    const int8_t* a;
+    const int8_t* a_lo;
+    const float* sa;
+    const int8_t* b;
+    const float* sb;
+    const void* bias;
+    const void* residual;
+    const void* rscale;
+    void* y;
+    int* dump;
+    int m, n, k, sms;
+};
+
+template <class T, int MODE, int BN, int CVT, bool DUMP>
+static int launch(const GemmArgs& g, cudaStream_t stream) {
+    using S = Shape<MODE, BN>;
+    auto kernel = gemm_i8_tc<T, MODE, BN, CVT, DUMP>;
+    static bool configured[64] = {};  // the attribute belongs to a device's copy of the kernel
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device < 0 || device >= 64 || !configured[device]) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes);
+        if (e != cudaSuccess) return int(e);
+        if (device >= 0 && device < 64) configured[device] = true;
+    }
+    if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15) || (g.a_lo && (reinterpret_cast<uintptr_t>(g.a_lo) & 15)))
+        return -2;
+    CUtensorMap map_a, map_a_lo, map_b;
+    if (!make_map(&map_a, g.a, g.m, g.k, kBM) || !make_map(&map_b, g.b, g.n, g.k, BN)) return int(cudaErrorNotSupported);
+    if (S::kHilo) {
+        if (!make_map(&map_a_lo, g.a_lo, g.m, g.k, kBM)) return int(cudaErrorNotSupported);
+    } else {
+        map_a_lo = map_a;
+    }
+    GemmParams p{};
+    p.sa = g.sa; p.sb = g.sb; p.bias = g.bias; p.residual = g.residual; p.rscale = g.rscale; p.y = g.y; p.dump = g.dump;
+    p.m = g.m; p.n = g.n; p.k = g.k;
+    p.tiles_m = (g.m + kBM - 1) / kBM;
+    p.tiles_n = (g.n + BN - 1) / BN;
+    p.vector_io = g.n % 8 == 0 && (reinterpret_cast<uintptr_t>(g.y) & 15) == 0 && (reinterpret_cast<uintptr_t>(g.residual) & 15) == 0;
+    const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
+    const int sms = g.sms > 0 ? g.sms : 148;
+    const int grid = int(tiles < sms ? tiles : sms);
+    kernel<<<grid, kThreads, S::kSmemBytes, stream>>>(map_a, map_a_lo, map_b, p);
+    return int(cudaGetLastError());
+}
+
+template <class T> static int dispatch(const GemmArgs& g, int variant, cudaStream_t stream) {
+    switch (variant) {
+        case 0: case 2: case 6: return launch<T, kRow, 256, 1, false>(g, stream);
+        case 1: case 7: return launch<T, kExact, 256, 1, false>(g, stream);
+        case 10: return launch<T, kBlock, 256, 0, false>(g, stream);
+        case 11: return launch<T, kBlock, 256, 1, false>(g, stream);
+        case 12: return launch<T, kBlockG, 256, 0, false>(g, stream);
+        case 13: return launch<T, kBlockG, 256, 1, false>(g, stream);
+        case 14: return launch<T, kExactG, 128, 1, false>(g, stream);
+    }
+    return -3;
+}
+
+}  // namespace wq
+
+using namespace wq;
+
+WQ_API int wq8_gemm(const int8_t* a, const int8_t* a_lo, const float* sa, const int8_t* b, const float* sb, const void* bias, const void* residual,
+                    const void* rscale, void* y, int m, int n, int k, int dtype, int variant, int sms, int /*split*/, int* /*workspace*/,
+                    int* /*counters*/, cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if ((variant == 1 || variant == 7 || variant == 14) != (a_lo != nullptr)) return -2;
+    if (k <= 0 || k % 16) return -2;
+    const GemmArgs g{a, a_lo, sa, b, sb, bias, residual, rscale, y, nullptr, m, n, k, sms};
+    if (dtype == 0) return dispatch<__half>(g, variant, stream);
+    if (dtype == 1) return dispatch<bf16>(g, variant, stream);
+    return -1;
+}
+
+// Whole tiles only: no partial-sum workspace, no counters.
+WQ_API void wq8_gemm_workspace(int, int, int, int, int, int, int64_t* sizes) { sizes[0] = sizes[1] = 0; }
+
+WQ_API int wq8_gemm_select(int, int, int, int hilo, int) { return hilo ? 1 : 0; }
+
+WQ_API int wq8_gemm_segments(const int8_t*, const int8_t*, const float*, const int8_t* const*, const float* const*, const void* const*, void* const*,
+                             int, int, int, int, int, int, int, int, int*, int*, cudaStream_t) {
+    return -4;
+}
+
+WQ_API int wq8_debug_block_sums(const int8_t* a, const int8_t* b, int32_t* sums, int m, int n, int k, int sms, cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (k <= 0 || k % 16) return -2;
+    const GemmArgs g{a, nullptr, nullptr, b, nullptr, nullptr, nullptr, nullptr, nullptr, sums, m, n, k, sms};
+    return launch<bf16, kBlock, 256, 1, true>(g, stream);
+}
+
+WQ_API int wq8_debug_status() {
+    int code = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&code, g_status, sizeof(int)) != cudaSuccess) return -1;
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    return code;
+}

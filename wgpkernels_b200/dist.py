@@ -1,0 +1,102 @@
+"""Output-channel (N) sharding of the INT8 linear over the GPUs of one node: one process per GPU, `torch.distributed` (NCCL over
+NVLink / NVSwitch) for the one exchange step.
+
+The reference is single-GPU; this is an addition.  Rank r keeps rows [r N / g, (r + 1) N / g) of the INT8 weight with their scales
+and bias (loaded once; the weight never moves).  The activation is present on every rank (replicated by the caller, or broadcast from
+rank 0 here); every rank quantizes it itself -- recomputing the quantization costs less than moving the INT8 copy over NVLink -- and
+runs the GEMM on its own output channels.  The one collective is the all-gather of the (M, N / g) output slices.
+
+Whether sharding pays is a property of the shape: the GEMM shrinks by g but every rank must receive (g - 1) / g of the (M, N) output,
+so `worth_sharding()` compares the two and `ShardedLinear` can keep the output sharded (`gather=None`) for a consumer that is sharded
+the same way (attention heads of a fused QKV projection).
+"""
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(n, world_size, rank, multiple=8):
+    """[start, stop) of rank's output channels: equal slices, each a multiple of `multiple` channels (the GEMM stores 16 bytes at a
+    time), the remainder going to the last rank."""
+    if n % multiple:
+        raise ValueError(f"N = {n} must be a multiple of {multiple} to be sharded")
+    units = n // multiple
+    per_rank = -(-units // world_size)
+    start = min(rank * per_rank, units) * multiple
+    stop = min((rank + 1) * per_rank, units) * multiple
+    return start, stop
+
+
+def worth_sharding(m, n, k, world_size, tops=2500.0, link_gbs=770.0, output_bytes=2):
+    """Estimated times in ms of the unsharded linear and of the sharded one with its all-gather, and whether sharding wins.
+    tops: sustained INT8 throughput of one GPU; link_gbs: per-direction NVLink bandwidth of one GPU."""
+    gemm_ms = 2.0 * m * n * k / (tops * 1e12) * 1e3
+    gather_ms = (world_size - 1) / world_size * m * n * output_bytes / (link_gbs * 1e9) * 1e3
+    sharded_ms = max(gemm_ms / world_size, gather_ms)  # the gather of finished row bands overlaps the GEMM of the next ones
+    return {"single_ms": gemm_ms, "sharded_ms": sharded_ms, "gather_ms": gather_ms, "shard": sharded_ms < gemm_ms}
+
+
+@dataclass
+class ShardedLinear:
+    """The rank's slice of one INT8 linear.  weight (N_local, K) int8, scale (N_local,) or (N_local, ceil(K / 128)) fp32, bias (N_local,).
+    linear: the local operator, `wgpkernels_b200.int8.linear` by default (injected so that the partition and gather logic can be tested
+    with CPU ranks)."""
+    weight: torch.Tensor
+    scale: torch.Tensor
+    bias: torch.Tensor = None
+    n_total: int = 0
+    group: object = None  # torch.distributed process group (None: the default group)
+    linear: object = None
+
+    def __post_init__(self):
+        self.world_size = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
+        self.n_total = self.n_total or self.weight.shape[0] * self.world_size
+        self.start, self.stop = shard_bounds(self.n_total, self.world_size, self.rank)
+        if self.stop - self.start != self.weight.shape[0]:
+            raise ValueError(f"rank {self.rank} holds {self.weight.shape[0]} channels, its slice is [{self.start}, {self.stop})")
+        equal = self.n_total % (8 * self.world_size) == 0
+        if not equal:
+            raise ValueError("N must split into equal slices of a multiple of 8 channels (all_gather moves equal chunks)")
+        if self.linear is None:
+            from wgpkernels_b200 import int8
+            self.linear = int8.linear
+        self._gathered = None
+
+    @classmethod
+    def from_full(cls, weight, scale, bias=None, group=None, linear=None):
+        """Slices an unsharded weight (every rank passes the same full tensors; only the slice is kept)."""
+        world_size = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        start, stop = shard_bounds(weight.shape[0], world_size, rank)
+        return cls(weight[start:stop].contiguous(), scale[start:stop].contiguous(), None if bias is None else bias[start:stop].contiguous(),
+                   weight.shape[0], group, linear)
+
+    def local(self, x, residual=None, residual_scale=None, **kwargs):
+        """This rank's output columns (M, N_local).  residual / residual_scale: the rank's own columns."""
+        return self.linear(x, self.weight, self.scale, self.bias, residual=residual, residual_scale=residual_scale, **kwargs)
+
+    def __call__(self, x, gather="full", broadcast_input=False, residual=None, residual_scale=None, **kwargs):
+        """gather: 'full' -> (M, N) on every rank; 'blocked' -> (g, M, N / g), rank-major (what the all-gather delivers, no extra copy);
+        None -> the local (M, N / g) slice only.  broadcast_input: x is valid on rank 0 only and is broadcast first."""
+        if broadcast_input and self.world_size > 1:
+            dist.broadcast(x, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0, group=self.group)
+        y = self.local(x, residual=residual, residual_scale=residual_scale, **kwargs)
+        if gather is None or self.world_size == 1:
+            return y if gather != "blocked" else y.unsqueeze(0)
+        m, n_local = y.shape
+        if self._gathered is None or self._gathered.shape != (self.world_size, m, n_local) or self._gathered.dtype != y.dtype:
+            self._gathered = torch.empty((self.world_size, m, n_local), dtype=y.dtype, device=y.device)
+        dist.all_gather_into_tensor(self._gathered.view(self.world_size * m, n_local), y.contiguous(), group=self.group)
+        if gather == "blocked":
+            return self._gathered
+        return unshard(self._gathered)
+
+
+def unshard(blocked, out=None):
+    """(g, M, N / g) rank-major slices -> (M, N) row-major."""
+    g, m, n_local = blocked.shape
+    out = torch.empty((m, g * n_local), dtype=blocked.dtype, device=blocked.device) if out is None else out
+    out.view(m, g, n_local).copy_(blocked.permute(1, 0, 2))
+    return out

@@ -21,6 +21,11 @@ from typing import Optional
 import torch
 
 
+# (M, K, N) of each configuration at full size
+SHAPES = {"c0": (64, 5120, 5120), "c1": (32760, 5120, 15360), "c2": (32760, 13824, 5120), "c3u": (1, 4096, 28672), "c3d": (1, 14336, 4096),
+          "c4": (16384, 3072, 12288)}
+
+
 @dataclass
 class Workload:
     name: str
