@@ -37,6 +37,7 @@ if str(ROOT) not in sys.path:
 from wgpkernels_b200 import workloads  # noqa: E402
 
 METRIC, UNIT = "int8_linear_effective_tops", "TOPS"
+FEW_TOKEN = {"c3u": "SwiGLU MLP up projection: K=4096 N=28672", "c3d": "SwiGLU MLP down projection: K=14336 N=4096, act=swiglu on a (M, 28672) input"}
 DESCRIPTIONS = {
     "c1": "block path, fused QKV projection of a 14B video DiT: M=32760 K=5120 N=15360, act=rms_norm, bf16 out",
     "c2": "block path, FFN down projection: M=32760 K=13824 N=5120, act=gelu, in-place residual, bf16 out",
@@ -121,18 +122,74 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_few_tokens(args, rank):
+    """Weight-streaming paths (BASELINE config 3): achieved HBM GB/s of one linear at 1-32 tokens, replicas only (rank 0 measures).
+    The weights (59-117 MB) would fit the 126 MB L2, so L2 is flushed before every timed launch and each launch has its own events."""
+    if rank != 0:
+        return
+    from wgpkernels_b200 import int8 as wq
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    wq.load_library()
+    m = args.tokens
+    path = args.path or ("lines" if m <= 4 else "small")
+    c = workloads.make(args.workload, rows=m)
+    g = c.to(device)
+    lib, stream = wq._require(), wq._stream(device)
+    flush_bytes = 2 * torch.cuda.get_device_properties(device).L2_cache_size
+
+    def launch():
+        return wq.linear(g.x, g.weight, g.scale, None, mode=path, act=c.act, precise=True)
+
+    for _ in range(max(args.warmup, 3)):
+        launch()
+    sampler = ClockSampler(0)
+    times = []
+    for _ in range(args.steps):
+        wq._check(lib.wq8_l2_flush(0, flush_bytes, stream))
+        first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        first.record()
+        launch()
+        last.record()
+        last.synchronize()
+        times.append(first.elapsed_time(last))
+    lib.wq8_l2_flush_release()
+    clocks = sampler.stop()
+    ms = sorted(times)[len(times) // 2]
+    n, k = c.n, c.k
+    # algorithmic bytes of one call: weights once, scales, activations in, outputs out (the swiglu transform reads 2 x and writes 1 x more)
+    moved = n * k + 4 * n + 2 * m * k + 2 * m * n + (6 * m * k if c.act == "swiglu" else 0)
+    if path == "exact":
+        moved += 3 * m * k  # the hi / lo INT8 copies written and read
+    peaks = measured_peaks()
+    peak = peaks["hbm_gbs"] if peaks else 6650.0
+    achieved = moved / (ms * 1e-3) / 1e9
+    line = {"metric": f"int8_{path}_weight_stream_gbs", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "replicas only", "vs_baseline": None, "dtype": "bf16 x int8 -> f32" if path != "exact" else "int8",
+            "data": "synthetic", "config": {"workload": f"{args.workload}: {FEW_TOKEN[args.workload]}", "tokens": m, "path": path,
+                                            "l2": "flushed before every timed launch (read of 2 x L2 bytes)"},
+            "effective_tops": 2 * m * n * k / (ms * 1e-3) / 1e12, "gpu_launches": args.steps * (2 if c.act or path == "exact" else 1), "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "algorithmic_bytes": moved, "peak_source": "MEASURED_PEAKS hbm_gbs, of measured" if peaks else "of fallback"}}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
-    parser.add_argument("--workload", default="c1", choices=sorted(DESCRIPTIONS))
+    parser.add_argument("--workload", default="c1", choices=sorted(DESCRIPTIONS) + sorted(FEW_TOKEN))
+    parser.add_argument("--tokens", type=int, default=1, help="token count of the few-token workloads (c3u, c3d)")
+    parser.add_argument("--path", default=None, help="path of the few-token workloads: lines, small or exact (default: by token count)")
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
     args = parser.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    if args.workload in FEW_TOKEN:
+        return run_few_tokens(args, rank)
     if args.impl == "reference":
         return run_reference(args, rank)
 

@@ -105,6 +105,11 @@ void wq8_l2_flush_release(void);
  * tests use to check the INT32 sums bit for bit. */
 int wq8_debug_block_sums(const int8_t* a, const int8_t* b, int32_t* sums, int m, int n, int k, int sms, wq8_stream_t stream);
 
+/* Issue-rate probe of the tensor pipe (kind 0: tcgen05 kind::i8, 1: kind::f16 with BF16): `iters` groups of four M128 N256 MMAs per SM on
+ * resident operands.  results[0] = TOPS of the whole GPU, [1] = SM MHz during the probe, [2] = clocks per group.  Allocates and frees a
+ * small buffer and synchronizes the device: a measurement tool, not part of the linear. */
+int wq8_debug_mma_peak(int kind, int iters, int sms, double* results);
+
 /* Device-side status word of the GEMM pipeline on the current device: 0, or a code left by a bounded wait
  * that gave up (the kernel then returned early with unspecified output).  Synchronizes the device; clears
  * the word.  For tests and diagnostics only. */

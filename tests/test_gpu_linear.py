@@ -68,7 +68,9 @@ def test_few_token_config(wq):
             g = c.to("cuda")
             y = wq.linear(g.x, g.weight, g.scale, None, mode=path, act=c.act, precise=True)
             reference = oracle.linear_reference(c.x, c.weight, c.scale, None, 0, c.act, None, 0.0, None, None, path in ("lines", "small"))
-            assert rel(y, reference) < (2e-3 if path == "exact" else 1e-3), (name, m, path)
+            # the output is rounded to bf16 (2^-9 relative per element); the FP32 reference is not
+            assert rel(y, reference) < 4e-3, (name, m, path)
+            assert rel(y, oracle.linear(path, c.x, c.weight.numpy(), c.scale.numpy(), None, 0, c.act)) < 1e-3, (name, m, path)
 
 
 def test_choose_path_and_cache(wq, tmp_path, monkeypatch):

@@ -45,14 +45,17 @@ WQ_DEVICE void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 WQ_DEVICE void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+// One potentially blocking test of the phase: the hardware may suspend the thread for up to `kSuspendNs` (it resumes as soon as the
+// phase completes), so a waiting role does not spend its scheduler's issue slots on polling.
+constexpr uint32_t kSuspendNs = 4000;
 WQ_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kSuspendNs)
         : "memory");
     return done != 0;
 }
@@ -115,15 +118,8 @@ WQ_DEVICE void tmem_load_32(uint32_t taddr, int* v) {
         : "memory");
 }
 #undef WQ_R4
-// Completes the loads above.  The registers are operands so that no use of them can be scheduled before the wait.
-#define WQ_RW4(a, i) "+r"(a[i]), "+r"(a[i + 1]), "+r"(a[i + 2]), "+r"(a[i + 3])
-WQ_DEVICE void tmem_load_wait(int* v) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : WQ_RW4(v, 0), WQ_RW4(v, 4), WQ_RW4(v, 8), WQ_RW4(v, 12), WQ_RW4(v, 16), WQ_RW4(v, 20), WQ_RW4(v, 24), WQ_RW4(v, 28)
-                 :
-                 : "memory");
-}
-#undef WQ_RW4
+// Completes the loads issued before it (the toolchain tracks tcgen05.ld destinations until this instruction).
+WQ_DEVICE void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
 WQ_DEVICE uint64_t smem_descriptor(uint32_t address) {
@@ -137,11 +133,27 @@ WQ_DEVICE uint64_t smem_descriptor(uint32_t address) {
 // Instruction descriptor: INT32 accumulator, signed INT8 A and B, both K-major, M = 128, N = n.
 __host__ __device__ constexpr uint32_t instruction_descriptor(int n) { return (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(kBM >> 4) << 24); }
 
-// Exact INT32 -> FP32 of a block sum.  |sum| <= 128 * 127 * 127 < 2^22, so adding it to the bits of 1.5 * 2^23 gives the float
-// 1.5 * 2^23 + sum exactly and one subtraction recovers it; CVT selects the conversion instruction instead.
-template <int CVT> WQ_DEVICE float block_sum_to_float(int s) {
-    if constexpr (CVT) return __int2float_rn(s);
-    return __int_as_float(s + 0x4B400000) - 12582912.f;
+// v[0..7] into the 32 columns starting at taddr of this thread's lane, eight columns per instruction (the source of a tensor-memory
+// store is a run of consecutive registers: eight stay resident instead of thirty-two).
+WQ_DEVICE void tmem_store_32(uint32_t taddr, const int* v) {
+#pragma unroll
+    for (int part = 0; part < 4; ++part)
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr + part * 8), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                     "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                     : "memory");
+}
+WQ_DEVICE void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Exact INT32 -> FP32 of block sums.  |sum| <= 128 * 127 * 127 < 2^22, so the bits of 1.5 * 2^23 plus the sum are the float
+// 1.5 * 2^23 + sum exactly and one subtraction recovers the sum (the conversion instruction issues at a quarter of that rate).
+// kFoldBiased: the accumulators in tensor memory START at those bits (the epilogue re-arms every column it drains), so the MMAs
+// themselves deliver the biased value and no integer add is needed.  kFoldAdd: the accumulators start at zero and the bits are added here.
+constexpr int kBiasBits = 0x4B400000;
+constexpr float kBiasValue = 12582912.f;
+enum Fold : int { kFoldBiased = 0, kFoldAdd = 1 };
+template <int FOLD> WQ_DEVICE float block_sum_to_float(int s) {
+    if constexpr (FOLD == kFoldAdd) s += kBiasBits;
+    return __int_as_float(s) - kBiasValue;
 }
 
 template <int MODE, int BN> struct Shape {
@@ -182,7 +194,7 @@ template <int BN> WQ_DEVICE TileCoord tile_origin(int t, int tiles_m, int tiles_
     return {(first + (t % width) % rows) * kBM, ((t % width) / rows) * BN};
 }
 
-template <class T, int MODE, int BN, int CVT, bool DUMP>
+template <class T, int MODE, int BN, int FOLD, bool DUMP>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b,
            const GemmParams p) {
@@ -227,6 +239,21 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
+    constexpr bool kBiased = S::kFold && FOLD == kFoldBiased && !DUMP;
+    if constexpr (kBiased) {
+        // arm every accumulator column with the bias bits once; from here on each drain re-arms what it read
+        if (warp >= 4) {
+            const int bias_run[8] = {kBiasBits, kBiasBits, kBiasBits, kBiasBits, kBiasBits, kBiasBits, kBiasBits, kBiasBits};
+            const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + ((warp - 4) >> 2) * kEpi;
+            for (int buffer = 0; buffer < kAccBuffers; ++buffer)
+                for (int part = 0; part < (S::kHilo ? 2 : 1); ++part)
+                    for (int chunk = 0; chunk < kEpi / 32; ++chunk) tmem_store_32(lane_addr + buffer * S::kAccColumns + part * BN + chunk * 32, bias_run);
+            tmem_store_wait();
+        }
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+    }
 
     // Registers move from the four control warps to the eight epilogue warps, which hold a tile's FP32 accumulators:
     // 128 x 56 + 256 x 224 = 64512 registers, what 384 threads x 168 were launched with.
@@ -278,7 +305,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     const uint32_t d = tmem_base + acc * S::kAccColumns;
 #pragma unroll
                     for (int j = 0; j < kStageK / kMmaK; ++j) {
-                        const uint32_t accumulate = (new_acc && j == 0) ? 0u : 1u;
+                        const uint32_t accumulate = (!kBiased && new_acc && j == 0) ? 0u : 1u;
                         const uint64_t step = uint64_t(j * kMmaK >> 4);  // start address advances in 16-byte units inside the swizzle row
                         mma_i8(d, a_desc + step, b_desc + step, idesc, accumulate);
                         if (S::kHilo) mma_i8(d + BN, a_lo_desc + step, b_desc + step, idesc, accumulate);
@@ -325,6 +352,11 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         int acc = 0, slot = 0;
         uint32_t acc_phase = 0, ring_phase = 0;
         bool ok = true;
+        // eight registers holding the bias bits for the whole kernel: opaque to the compiler, which would otherwise rebuild the
+        // constants (eight moves) in front of every tensor-memory store
+        int bias_run[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) asm volatile("mov.b32 %0, %1;" : "=r"(bias_run[j]) : "r"(kBiasBits));
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
             const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n);
             const int row = c.m0 + quarter * 32 + lane;
@@ -401,33 +433,45 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     tc_fence_after();
                     const uint32_t taddr = tmem_base + lane_base + acc * S::kAccColumns + half * kEpi;
                     const float* ring = scale_ring + slot * BN + half * kEpi;
+                    // the loads of chunk c + 1 are in flight while chunk c is folded
+                    int s_hi[2][32], s_lo[2][32];
+                    tmem_load_32(taddr, s_hi[0]);
+                    if (S::kHilo) tmem_load_32(taddr + BN, s_lo[0]);
 #pragma unroll
                     for (int chunk = 0; chunk < kEpi / 32; ++chunk) {
-                        int s_hi[32], s_lo[32];
-                        tmem_load_32(taddr + chunk * 32, s_hi);
-                        if (S::kHilo) tmem_load_32(taddr + BN + chunk * 32, s_lo);
-                        tmem_load_wait(s_hi);
-                        if (S::kHilo) tmem_load_wait(s_lo);
+                        int* hi = s_hi[chunk & 1];
+                        int* lo = s_lo[chunk & 1];
+                        tmem_load_wait();
+                        if (chunk + 1 < kEpi / 32) {
+                            tmem_load_32(taddr + (chunk + 1) * 32, s_hi[(chunk + 1) & 1]);
+                            if (S::kHilo) tmem_load_32(taddr + BN + (chunk + 1) * 32, s_lo[(chunk + 1) & 1]);
+                        }
+                        if constexpr (kBiased) {
+                            tmem_store_32(taddr + chunk * 32, bias_run);
+                            if (S::kHilo) tmem_store_32(taddr + BN + chunk * 32, bias_run);
+                        }
                         if constexpr (DUMP) {
                             if (row_ok)
 #pragma unroll
                                 for (int j = 0; j < 32; ++j)
-                                    if (col0 + chunk * 32 + j < p.n) p.dump[(int64_t(kb) * p.m + row) * p.n + col0 + chunk * 32 + j] = s_hi[j];
-                        }
+                                    if (col0 + chunk * 32 + j < p.n) p.dump[(int64_t(kb) * p.m + row) * p.n + col0 + chunk * 32 + j] = hi[j];
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            float* a = &accf[chunk * 32 + j];
-                            if constexpr (MODE == kBlock) {
-                                *a = fmaf(block_sum_to_float<CVT>(s_hi[j]), sa_now, *a);
-                            } else if constexpr (MODE == kBlockG) {
-                                *a = fmaf(block_sum_to_float<CVT>(s_hi[j]), sa_now * ring[chunk * 32 + j], *a);
-                            } else {
-                                const float v = fmaf(block_sum_to_float<CVT>(s_lo[j]), 1.f / 254.f, block_sum_to_float<CVT>(s_hi[j]));
-                                *a = fmaf(v, ring[chunk * 32 + j], *a);
+                            for (int j = 0; j < 32; ++j) {
+                                float* a = &accf[chunk * 32 + j];
+                                const float v = block_sum_to_float<FOLD>(hi[j]);
+                                if constexpr (MODE == kBlock) {
+                                    *a = fmaf(v, sa_now, *a);
+                                } else if constexpr (MODE == kBlockG) {
+                                    *a = fmaf(v, sa_now * ring[chunk * 32 + j], *a);
+                                } else {
+                                    *a = fmaf(fmaf(block_sum_to_float<FOLD>(lo[j]), 1.f / 254.f, v), ring[chunk * 32 + j], *a);
+                                }
                             }
                         }
                     }
                     // this warp is done with the accumulator buffer (and the scale slot): hand them back
+                    if constexpr (kBiased) tmem_store_wait();
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {
@@ -453,8 +497,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     int s_hi[32], s_lo[32];
                     tmem_load_32(taddr + chunk * 32, s_hi);
                     if (S::kHilo) tmem_load_32(taddr + BN + chunk * 32, s_lo);
-                    tmem_load_wait(s_hi);
-                    if (S::kHilo) tmem_load_wait(s_lo);
+                    tmem_load_wait();
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -478,6 +521,65 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     tc_fence_before();
     __syncthreads();
     if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
+// Issue-rate probe of the tensor pipe: one CTA per SM issues `iters` groups of four M128 N256 MMAs on resident shared-memory
+// operands (no loads, no epilogue), alternating the two accumulator buffers.  KIND 0: kind::i8 (K = 32), 1: kind::f16 with BF16 (K = 16).
+template <int KIND>
+__global__ void __launch_bounds__(128, 1) mma_peak_probe(int iters, long long* cycles, long long* nanoseconds) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint32_t tmem_slot;
+    __shared__ uint64_t bar;
+    __shared__ int abort_word;
+    for (int i = threadIdx.x; i < (kBM + 256) * kStageK / 16; i += blockDim.x) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (threadIdx.x == 0) {
+        abort_word = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the zeroes above are read by the tensor cores
+    if (threadIdx.x < 32) tmem_alloc(smem_u32(&tmem_slot), kTmemColumns);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    if (threadIdx.x == 0) {
+        // KIND 1: F32 accumulator (1 << 4), BF16 A and B (1 << 7, 1 << 10)
+        constexpr uint32_t idesc = KIND == 0 ? instruction_descriptor(256)
+                                             : ((1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(256 >> 3) << 17) | (uint32_t(kBM >> 4) << 24));
+        const uint64_t a_desc = smem_descriptor(smem_u32(smem)), b_desc = smem_descriptor(smem_u32(smem) + kBM * kStageK);
+        long long t0 = clock64(), g0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g0));
+        for (int i = 0; i < iters; ++i) {
+            const uint32_t d = tmem_base + (i & 1) * 256;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (KIND == 0) {
+                    mma_i8(d, a_desc + 2 * j, b_desc + 2 * j, idesc, 1u);
+                } else {
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\t"
+                        "setp.ne.b32 p, %4, 0;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d),
+                        "l"(a_desc + 2 * j), "l"(b_desc + 2 * j), "r"(idesc), "r"(1u)
+                        : "memory");
+                }
+            }
+        }
+        tc_commit(smem_u32(&bar));
+        mbar_wait(smem_u32(&bar), 0, &abort_word, kTimeoutTmemFull);
+        long long t1 = clock64(), g1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
+        cycles[blockIdx.x] = t1 - t0;
+        nanoseconds[blockIdx.x] = g1 - g0;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x < 32) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemColumns);
     }
@@ -524,10 +626,10 @@ struct GemmArgs {
     int m, n, k, sms;
 };
 
-template <class T, int MODE, int BN, int CVT, bool DUMP>
+template <class T, int MODE, int BN, int FOLD, bool DUMP>
 static int launch(const GemmArgs& g, cudaStream_t stream) {
     using S = Shape<MODE, BN>;
-    auto kernel = gemm_i8_tc<T, MODE, BN, CVT, DUMP>;
+    auto kernel = gemm_i8_tc<T, MODE, BN, FOLD, DUMP>;
     static bool configured[64] = {};  // the attribute belongs to a device's copy of the kernel
     int device = 0;
     cudaGetDevice(&device);
@@ -560,13 +662,13 @@ static int launch(const GemmArgs& g, cudaStream_t stream) {
 
 template <class T> static int dispatch(const GemmArgs& g, int variant, cudaStream_t stream) {
     switch (variant) {
-        case 0: case 2: case 6: return launch<T, kRow, 256, 1, false>(g, stream);
-        case 1: case 7: return launch<T, kExact, 256, 1, false>(g, stream);
-        case 10: return launch<T, kBlock, 256, 0, false>(g, stream);
-        case 11: return launch<T, kBlock, 256, 1, false>(g, stream);
-        case 12: return launch<T, kBlockG, 256, 0, false>(g, stream);
-        case 13: return launch<T, kBlockG, 256, 1, false>(g, stream);
-        case 14: return launch<T, kExactG, 128, 1, false>(g, stream);
+        case 0: case 2: case 6: return launch<T, kRow, 256, kFoldAdd, false>(g, stream);
+        case 1: case 7: return launch<T, kExact, 256, kFoldAdd, false>(g, stream);
+        case 10: return launch<T, kBlock, 256, kFoldBiased, false>(g, stream);
+        case 11: return launch<T, kBlock, 256, kFoldAdd, false>(g, stream);
+        case 12: return launch<T, kBlockG, 256, kFoldBiased, false>(g, stream);
+        case 13: return launch<T, kBlockG, 256, kFoldAdd, false>(g, stream);
+        case 14: return launch<T, kExactG, 128, kFoldBiased, false>(g, stream);
     }
     return -3;
 }
@@ -601,7 +703,31 @@ WQ_API int wq8_debug_block_sums(const int8_t* a, const int8_t* b, int32_t* sums,
     if (m <= 0 || n <= 0) return 0;
     if (k <= 0 || k % 16) return -2;
     const GemmArgs g{a, nullptr, nullptr, b, nullptr, nullptr, nullptr, nullptr, nullptr, sums, m, n, k, sms};
-    return launch<bf16, kBlock, 256, 1, true>(g, stream);
+    return launch<bf16, kBlock, 256, kFoldAdd, true>(g, stream);
+}
+
+// results[0] = tera-operations per second of the whole GPU, results[1] = SM clock in MHz during the probe, results[2] = clocks per MMA group.
+WQ_API int wq8_debug_mma_peak(int kind, int iters, int sms, double* results) {
+    if (iters <= 0 || sms <= 0 || sms > 1024 || (kind != 0 && kind != 1)) return -2;
+    long long* buffers = nullptr;
+    if (cudaMalloc(&buffers, sizeof(long long) * 2 * sms) != cudaSuccess) return int(cudaGetLastError());
+    const int smem_bytes = (kBM + 256) * kStageK + 1024;
+    auto kernel = kind == 0 ? mma_peak_probe<0> : mma_peak_probe<1>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    for (int round = 0; round < 2; ++round) kernel<<<sms, 128, smem_bytes>>>(iters, buffers, buffers + sms);
+    int code = int(cudaDeviceSynchronize());
+    long long host[2048];
+    if (!code) code = int(cudaMemcpy(host, buffers, sizeof(long long) * 2 * sms, cudaMemcpyDeviceToHost));
+    cudaFree(buffers);
+    if (code) return code;
+    double cycles = 0, ns = 0;
+    for (int i = 0; i < sms; ++i) { cycles += double(host[i]); ns += double(host[sms + i]); }
+    cycles /= sms; ns /= sms;
+    const double ops = 2.0 * kBM * 256 * (kind == 0 ? 32 : 16) * 4.0 * iters * sms;
+    results[0] = ops / (ns * 1e-9) / 1e12;
+    results[1] = cycles / ns * 1e3;
+    results[2] = cycles / iters;
+    return 0;
 }
 
 WQ_API int wq8_debug_status() {
