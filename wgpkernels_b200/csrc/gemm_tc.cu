@@ -182,7 +182,7 @@ struct GemmParams {
     int* dump;  // debug: raw block sums (kblocks, M, N)
     int m, n, k;
     int tiles_m, tiles_n;
-    int vector_io;  // y / residual rows allow 16-byte accesses
+    int vector_io;  // y, residual, sb, bias and rscale allow 16-byte accesses (N multiple of 8, aligned bases)
 };
 
 struct TileCoord { int m0, n0; };
@@ -367,45 +367,58 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             // y values of 32 columns starting at `col`: bias, residual, one rounding, store
             auto emit = [&](const float* v, int col) {
                 if (!row_ok || col >= p.n) return;
-                float out[32];
+                T* dst = y + int64_t(row) * p.n + col;
+                const T* res = residual ? residual + int64_t(row) * p.n + col : nullptr;
+                if (p.vector_io && col + 32 <= p.n) {
+                    // whole chunk, every operand 16-byte aligned: eight outputs per step with 128-bit accesses
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        float scale8[8], bias8[8], out[8];
+                        if constexpr (S::kWGroup) {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) scale8[e] = 1.f;
+                        } else {
+                            const float4 s0 = __ldg(reinterpret_cast<const float4*>(p.sb + col + j)), s1 = __ldg(reinterpret_cast<const float4*>(p.sb + col + j) + 1);
+                            scale8[0] = s0.x; scale8[1] = s0.y; scale8[2] = s0.z; scale8[3] = s0.w;
+                            scale8[4] = s1.x; scale8[5] = s1.y; scale8[6] = s1.z; scale8[7] = s1.w;
+                        }
+                        load_eight(bias + col + j, bias8, bias != nullptr);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) out[e] = fmaf(v[j + e] * row_scale, scale8[e], bias8[e]);
+                        if (res) {
+                            float res8[8], rs8[8];
+                            const uint4 raw = *reinterpret_cast<const uint4*>(res + j);  // read before this thread overwrites it (y may be the residual)
+                            unpack_pair<T>(raw.x, res8[0], res8[1]);
+                            unpack_pair<T>(raw.y, res8[2], res8[3]);
+                            unpack_pair<T>(raw.z, res8[4], res8[5]);
+                            unpack_pair<T>(raw.w, res8[6], res8[7]);
+                            if (rscale) {
+                                load_eight(rscale + col + j, rs8, true);
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) rs8[e] = 1.f;
+                            }
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) out[e] = fmaf(out[e], rs8[e], res8[e]);
+                        }
+                        uint4 packed;
+                        packed.x = pack_pair<T>(out[0], out[1]);
+                        packed.y = pack_pair<T>(out[2], out[3]);
+                        packed.z = pack_pair<T>(out[4], out[5]);
+                        packed.w = pack_pair<T>(out[6], out[7]);
+                        *reinterpret_cast<uint4*>(dst + j) = packed;
+                    }
+                    return;
+                }
+                // ragged or unaligned: one element at a time (fully unrolled: the accumulators must stay in registers)
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int cj = col + j;
-                    const bool in = cj < p.n;
-                    const float col_scale = S::kWGroup ? 1.f : (in ? __ldg(p.sb + cj) : 0.f);
-                    const float b = bias && in ? as_float(bias[cj]) : 0.f;
-                    out[j] = fmaf(v[j] * row_scale, col_scale, b);
-                }
-                T* dst = y + int64_t(row) * p.n + col;
-                const T* res = residual ? residual + int64_t(row) * p.n + col : nullptr;
-                if (p.vector_io) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        if (col + j >= p.n) break;
-                        if (res) {
-                            const uint4 raw = *reinterpret_cast<const uint4*>(res + j);
-                            const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                float r0, r1;
-                                unpack_pair<T>(words[e], r0, r1);
-                                const int cj = col + j + 2 * e;
-                                out[j + 2 * e] = fmaf(out[j + 2 * e], rscale ? as_float(rscale[cj]) : 1.f, r0);
-                                out[j + 2 * e + 1] = fmaf(out[j + 2 * e + 1], rscale ? as_float(rscale[cj + 1]) : 1.f, r1);
-                            }
-                        }
-                        uint4 packed;
-                        packed.x = pack_pair<T>(out[j], out[j + 1]);
-                        packed.y = pack_pair<T>(out[j + 2], out[j + 3]);
-                        packed.z = pack_pair<T>(out[j + 4], out[j + 5]);
-                        packed.w = pack_pair<T>(out[j + 6], out[j + 7]);
-                        *reinterpret_cast<uint4*>(dst + j) = packed;
-                    }
-                } else {
-                    for (int j = 0; j < 32 && col + j < p.n; ++j) {
-                        float v1 = out[j];
-                        if (res) v1 = fmaf(v1, rscale ? as_float(rscale[col + j]) : 1.f, as_float(res[j]));
-                        dst[j] = round_one<T>(v1);
+                    if (cj < p.n) {
+                        const float col_scale = S::kWGroup ? 1.f : __ldg(p.sb + cj);
+                        float value = fmaf(v[j] * row_scale, col_scale, bias ? as_float(bias[cj]) : 0.f);
+                        if (res) value = fmaf(value, rscale ? as_float(rscale[cj]) : 1.f, as_float(res[j]));
+                        dst[j] = round_one<T>(value);
                     }
                 }
             };
@@ -652,7 +665,9 @@ static int launch(const GemmArgs& g, cudaStream_t stream) {
     p.m = g.m; p.n = g.n; p.k = g.k;
     p.tiles_m = (g.m + kBM - 1) / kBM;
     p.tiles_n = (g.n + BN - 1) / BN;
-    p.vector_io = g.n % 8 == 0 && (reinterpret_cast<uintptr_t>(g.y) & 15) == 0 && (reinterpret_cast<uintptr_t>(g.residual) & 15) == 0;
+    const uintptr_t bases = reinterpret_cast<uintptr_t>(g.y) | reinterpret_cast<uintptr_t>(g.residual) | reinterpret_cast<uintptr_t>(g.bias) |
+                            reinterpret_cast<uintptr_t>(g.rscale) | (S::kWGroup ? 0 : reinterpret_cast<uintptr_t>(g.sb));
+    p.vector_io = g.n % 8 == 0 && (bases & 15) == 0;
     const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
     const int sms = g.sms > 0 ? g.sms : 148;
     const int grid = int(tiles < sms ? tiles : sms);
