@@ -106,7 +106,7 @@ void wq8_l2_flush_release(void);
 int wq8_debug_block_sums(const int8_t* a, const int8_t* b, int32_t* sums, int m, int n, int k, int sms, wq8_stream_t stream);
 
 /* Issue-rate probe of the tensor pipe (kind 0: tcgen05 kind::i8, 1: kind::f16 with BF16): `iters` groups of four M128 N256 MMAs per SM on
- * resident operands.  results[0] = TOPS of the whole GPU, [1] = SM MHz during the probe, [2] = clocks per group.  Allocates and frees a
+ * resident operands (zeros; pseudo-random bytes when iters is negative).  results[0] = TOPS of the whole GPU, [1] = SM MHz during the probe, [2] = clocks per group.  Allocates and frees a
  * small buffer and synchronizes the device: a measurement tool, not part of the linear. */
 int wq8_debug_mma_peak(int kind, int iters, int sms, double* results);
 

@@ -29,7 +29,7 @@ def _stale(target, sources):
     return target.stat().st_mtime < newest
 
 
-def build(output=None, nvcc="nvcc", verbose=False, jobs=None, force=False):
+def build(output=None, nvcc="nvcc", verbose=False, jobs=None, force=False, defines=()):
     target = Path(output or library_file()).resolve()
     csrc = PACKAGE / "csrc"
     inputs = [csrc / name for name in SOURCES] + [csrc / "common.cuh"]
@@ -37,6 +37,7 @@ def build(output=None, nvcc="nvcc", verbose=False, jobs=None, force=False):
         return target
     target.parent.mkdir(parents=True, exist_ok=True)
     common = [nvcc, "-O3", "-std=c++17", "-lineinfo", *ARCH_FLAGS, "-Xcompiler", "-fPIC,-fvisibility=hidden", "--cudart", "static"]
+    common += [f"-D{name}" for name in defines]
     if verbose:
         common += ["-Xptxas", "-v"]
     with tempfile.TemporaryDirectory(prefix="wgpkernels-b200-") as work:
@@ -64,8 +65,9 @@ def main():
     parser.add_argument("--verbose", action="store_true", help="print register and shared memory usage (-Xptxas -v)")
     parser.add_argument("--jobs", type=int, default=None)
     parser.add_argument("--force", action="store_true")
+    parser.add_argument("--define", action="append", default=[], help="preprocessor symbol of a diagnostic build (NAME or NAME=VALUE)")
     args = parser.parse_args()
-    print(f"Built {build(args.output, args.nvcc, args.verbose, args.jobs, args.force)}")
+    print(f"Built {build(args.output, args.nvcc, args.verbose, args.jobs, args.force or bool(args.define), args.define)}")
 
 
 if __name__ == "__main__":

@@ -133,15 +133,16 @@ WQ_DEVICE uint64_t smem_descriptor(uint32_t address) {
 // Instruction descriptor: INT32 accumulator, signed INT8 A and B, both K-major, M = 128, N = n.
 __host__ __device__ constexpr uint32_t instruction_descriptor(int n) { return (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(kBM >> 4) << 24); }
 
-// v[0..7] into the 32 columns starting at taddr of this thread's lane, eight columns per instruction (the source of a tensor-memory
-// store is a run of consecutive registers: eight stay resident instead of thirty-two).
+// v[0..15] twice into the 32 columns starting at taddr of this thread's lane (sixteen source registers stay resident).
+#define WQ_IN4(a, i) "r"(a[i]), "r"(a[i + 1]), "r"(a[i + 2]), "r"(a[i + 3])
 WQ_DEVICE void tmem_store_32(uint32_t taddr, const int* v) {
 #pragma unroll
-    for (int part = 0; part < 4; ++part)
-        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr + part * 8), "r"(v[0]), "r"(v[1]), "r"(v[2]),
-                     "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+    for (int part = 0; part < 2; ++part)
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr + part * 16),
+                     WQ_IN4(v, 0), WQ_IN4(v, 4), WQ_IN4(v, 8), WQ_IN4(v, 12)
                      : "memory");
 }
+#undef WQ_IN4
 WQ_DEVICE void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Exact INT32 -> FP32 of block sums.  |sum| <= 128 * 127 * 127 < 2^22, so the bits of 1.5 * 2^23 plus the sum are the float
@@ -149,6 +150,15 @@ WQ_DEVICE void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;"
 // kFoldBiased: the accumulators in tensor memory START at those bits (the epilogue re-arms every column it drains), so the MMAs
 // themselves deliver the biased value and no integer add is needed.  kFoldAdd: the accumulators start at zero and the bits are added here.
 constexpr int kBiasBits = 0x4B400000;
+#define WQ_B4 kBiasBits, kBiasBits, kBiasBits, kBiasBits
+// The re-arming store takes its 16 source registers from here, through volatile loads: values the compiler cannot rebuild with moves in
+// front of every store (it would: a move per register and store), so they stay resident for the whole kernel.
+__device__ int g_bias_run[16] = {WQ_B4, WQ_B4, WQ_B4, WQ_B4};
+#undef WQ_B4
+WQ_DEVICE void load_bias_run(int* v) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) asm volatile("ld.volatile.global.b32 %0, [%1];" : "=r"(v[j]) : "l"(g_bias_run + j));
+}
 constexpr float kBiasValue = 12582912.f;
 enum Fold : int { kFoldBiased = 0, kFoldAdd = 1 };
 template <int FOLD> WQ_DEVICE float block_sum_to_float(int s) {
@@ -243,7 +253,8 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     if constexpr (kBiased) {
         // arm every accumulator column with the bias bits once; from here on each drain re-arms what it read
         if (warp >= 4) {
-            const int bias_run[8] = {kBiasBits, kBiasBits, kBiasBits, kBiasBits, kBiasBits, kBiasBits, kBiasBits, kBiasBits};
+            int bias_run[16];
+            load_bias_run(bias_run);
             const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + ((warp - 4) >> 2) * kEpi;
             for (int buffer = 0; buffer < kAccBuffers; ++buffer)
                 for (int part = 0; part < (S::kHilo ? 2 : 1); ++part)
@@ -352,11 +363,8 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         int acc = 0, slot = 0;
         uint32_t acc_phase = 0, ring_phase = 0;
         bool ok = true;
-        // eight registers holding the bias bits for the whole kernel: opaque to the compiler, which would otherwise rebuild the
-        // constants (eight moves) in front of every tensor-memory store
-        int bias_run[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) asm volatile("mov.b32 %0, %1;" : "=r"(bias_run[j]) : "r"(kBiasBits));
+        int bias_run[16];
+        if constexpr (kBiased) load_bias_run(bias_run);
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
             const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n);
             const int row = c.m0 + quarter * 32 + lane;
@@ -446,50 +454,72 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     tc_fence_after();
                     const uint32_t taddr = tmem_base + lane_base + acc * S::kAccColumns + half * kEpi;
                     const float* ring = scale_ring + slot * BN + half * kEpi;
-                    // the loads of chunk c + 1 are in flight while chunk c is folded
-                    int s_hi[2][32], s_lo[2][32];
-                    tmem_load_32(taddr, s_hi[0]);
-                    if (S::kHilo) tmem_load_32(taddr + BN, s_lo[0]);
-#pragma unroll
-                    for (int chunk = 0; chunk < kEpi / 32; ++chunk) {
-                        int* hi = s_hi[chunk & 1];
-                        int* lo = s_lo[chunk & 1];
-                        tmem_load_wait();
-                        if (chunk + 1 < kEpi / 32) {
-                            tmem_load_32(taddr + (chunk + 1) * 32, s_hi[(chunk + 1) & 1]);
-                            if (S::kHilo) tmem_load_32(taddr + BN + (chunk + 1) * 32, s_lo[(chunk + 1) & 1]);
-                        }
+                    // Two staging buffers of 32 columns.  The buffer in tensor memory is handed back as soon as its last column has been
+                    // read (and re-armed), half a drain before the folding ends: the MMAs of the block after next start that much earlier.
+                    int hi[2][32], lo[2][32];
+                    constexpr int kChunks = kEpi / 32;
+                    auto fetch = [&](int chunk) {
+                        tmem_load_32(taddr + chunk * 32, hi[chunk & 1]);
+                        if (S::kHilo) tmem_load_32(taddr + BN + chunk * 32, lo[chunk & 1]);
+                    };
+                    auto rearm = [&](int chunk) {
                         if constexpr (kBiased) {
                             tmem_store_32(taddr + chunk * 32, bias_run);
                             if (S::kHilo) tmem_store_32(taddr + BN + chunk * 32, bias_run);
                         }
+                    };
+                    auto release = [&]() {
+                        if constexpr (kBiased) tmem_store_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+                    };
+                    auto fold = [&](int chunk) {
+                        const int* h = hi[chunk & 1];
+                        const int* l = lo[chunk & 1];
                         if constexpr (DUMP) {
                             if (row_ok)
 #pragma unroll
                                 for (int j = 0; j < 32; ++j)
-                                    if (col0 + chunk * 32 + j < p.n) p.dump[(int64_t(kb) * p.m + row) * p.n + col0 + chunk * 32 + j] = hi[j];
+                                    if (col0 + chunk * 32 + j < p.n) p.dump[(int64_t(kb) * p.m + row) * p.n + col0 + chunk * 32 + j] = h[j];
                         } else {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
                                 float* a = &accf[chunk * 32 + j];
-                                const float v = block_sum_to_float<FOLD>(hi[j]);
+                                const float v = block_sum_to_float<FOLD>(h[j]);
                                 if constexpr (MODE == kBlock) {
                                     *a = fmaf(v, sa_now, *a);
                                 } else if constexpr (MODE == kBlockG) {
                                     *a = fmaf(v, sa_now * ring[chunk * 32 + j], *a);
                                 } else {
-                                    *a = fmaf(fmaf(block_sum_to_float<FOLD>(lo[j]), 1.f / 254.f, v), ring[chunk * 32 + j], *a);
+                                    *a = fmaf(fmaf(block_sum_to_float<FOLD>(l[j]), 1.f / 254.f, v), ring[chunk * 32 + j], *a);
                                 }
                             }
                         }
+                    };
+                    static_assert(kChunks >= 2 && kChunks % 2 == 0, "the drain works on pairs of 32-column chunks");
+                    fetch(0);
+                    fetch(1);
+                    tmem_load_wait();
+                    rearm(0);
+                    rearm(1);
+                    if (kChunks == 2) release();
+#pragma unroll
+                    for (int chunk = 0; chunk < kChunks; ++chunk) {
+                        fold(chunk);
+                        if (chunk + 2 < kChunks) {
+                            fetch(chunk + 2);  // into the staging buffer just folded
+                            if (chunk & 1) {   // chunks chunk + 1 and chunk + 2 are in flight: complete the pair
+                                tmem_load_wait();
+                                rearm(chunk + 1);
+                                rearm(chunk + 2);
+                                if (chunk + 2 == kChunks - 1) release();
+                            }
+                        }
                     }
-                    // this warp is done with the accumulator buffer (and the scale slot): hand them back
-                    if constexpr (kBiased) tmem_store_wait();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(bar_acc_empty + 8 * acc);
-                        if (S::kWGroup) mbar_arrive(bar_ring_empty + 8 * slot);
+                    if constexpr (S::kWGroup) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_ring_empty + 8 * slot);
                     }
                     if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1u; }
                     if (S::kWGroup && ++slot == kScaleRing) { slot = 0; ring_phase ^= 1u; }
@@ -548,7 +578,14 @@ __global__ void __launch_bounds__(128, 1) mma_peak_probe(int iters, long long* c
     __shared__ uint32_t tmem_slot;
     __shared__ uint64_t bar;
     __shared__ int abort_word;
-    for (int i = threadIdx.x; i < (kBM + 256) * kStageK / 16; i += blockDim.x) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
+    // operands: zeros (the quietest data) or pseudo-random bytes (iters < 0): the tensor pipe's power, and with it the clock, depends on them
+    const bool noisy = iters < 0;
+    if (noisy) iters = -iters;
+    for (int i = threadIdx.x; i < (kBM + 256) * kStageK / 16; i += blockDim.x) {
+        uint32_t h = (i * 4 + blockIdx.x * 7919u) * 2654435761u;
+        const uint4 v = make_uint4(h, h * 2246822519u, h * 3266489917u, h * 668265263u);
+        reinterpret_cast<uint4*>(smem)[i] = noisy ? v : make_uint4(0u, 0u, 0u, 0u);
+    }
     if (threadIdx.x == 0) {
         abort_word = 0;
         mbar_init(smem_u32(&bar), 1);
@@ -723,7 +760,7 @@ WQ_API int wq8_debug_block_sums(const int8_t* a, const int8_t* b, int32_t* sums,
 
 // results[0] = tera-operations per second of the whole GPU, results[1] = SM clock in MHz during the probe, results[2] = clocks per MMA group.
 WQ_API int wq8_debug_mma_peak(int kind, int iters, int sms, double* results) {
-    if (iters <= 0 || sms <= 0 || sms > 1024 || (kind != 0 && kind != 1)) return -2;
+    if (iters == 0 || sms <= 0 || sms > 1024 || (kind != 0 && kind != 1)) return -2;
     long long* buffers = nullptr;
     if (cudaMalloc(&buffers, sizeof(long long) * 2 * sms) != cudaSuccess) return int(cudaGetLastError());
     const int smem_bytes = (kBM + 256) * kStageK + 1024;
@@ -738,10 +775,10 @@ WQ_API int wq8_debug_mma_peak(int kind, int iters, int sms, double* results) {
     double cycles = 0, ns = 0;
     for (int i = 0; i < sms; ++i) { cycles += double(host[i]); ns += double(host[sms + i]); }
     cycles /= sms; ns /= sms;
-    const double ops = 2.0 * kBM * 256 * (kind == 0 ? 32 : 16) * 4.0 * iters * sms;
+    const double ops = 2.0 * kBM * 256 * (kind == 0 ? 32 : 16) * 4.0 * (iters < 0 ? -iters : iters) * sms;
     results[0] = ops / (ns * 1e-9) / 1e12;
     results[1] = cycles / ns * 1e3;
-    results[2] = cycles / iters;
+    results[2] = cycles / (iters < 0 ? -iters : iters);
     return 0;
 }
 
