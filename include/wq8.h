@@ -105,6 +105,16 @@ void wq8_l2_flush_release(void);
  * tests use to check the INT32 sums bit for bit. */
 int wq8_debug_block_sums(const int8_t* a, const int8_t* b, int32_t* sums, int m, int n, int k, int sms, wq8_stream_t stream);
 
+/* wq8_small for callers that cannot allocate device memory (no counterpart in the reference, which always takes caller scratch).
+ * A host that reaches this library through a bare FFI with buffers it was handed, a serving loop under a fixed memory budget, code
+ * running during CUDA graph capture or in a section where cudaMalloc is not allowed: none of them can supply the K-split scratch
+ * wq8_small asks for.  Here the scratch is a static device buffer inside the library (2 MiB + 4 KiB per GPU that loads it, held until
+ * the process exits); nothing is allocated or freed.  The first call on a device looks up the buffer's device address and should come
+ * before any stream capture.  Same arguments, values and error codes as wq8_small without `slots` / `counters`; -5 when the shape's
+ * scratch exceeds the buffer.  All calls on a device share the buffer: calls whose kernels can overlap on the GPU race. */
+int wq8_small_static(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
+                     void* y, int m, int n, int k, int dtype, int sms, wq8_stream_t stream);
+
 /* Issue-rate probe of the tensor pipe (kind 0: tcgen05 kind::i8, 1: kind::f16 with BF16): `iters` groups of four M128 N256 MMAs per SM on
  * resident operands (zeros; pseudo-random bytes when iters is negative).  results[0] = TOPS of the whole GPU, [1] = SM MHz during the probe, [2] = clocks per group.  Allocates and frees a
  * small buffer and synchronizes the device: a measurement tool, not part of the linear. */

@@ -304,3 +304,77 @@ WQ_API int wq8_gemv_lines(const void* x, int64_t ldx, const int8_t* w, const flo
     if (dtype == 0) return launch_cores<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, stream);
     return launch_cores<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, stream);
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// wq8_small without caller scratch.
+//
+// wq8_small splits K across CTAs when few output channels would leave SMs idle, and the caller has to hand it the partial-sum slots
+// and the tile counters for that.  Some callers have no way to provide them: a host that drives this library through plain ctypes / FFI
+// with buffers it was given (no allocator of its own on the device), a serving loop that runs under a fixed memory budget and may not
+// grow it per request, code that runs while a CUDA graph is being captured or inside a real-time section where cudaMalloc (which
+// synchronizes and may fail) is off limits.  For them the scratch lives here, in device memory that belongs to the library: every GPU
+// that loads the library holds kStaticScratchBytes (2 MiB + 4 KiB) of it until the process exits.
+//
+// The array's name is only a handle on the host: a kernel must be given the device address, which cudaGetSymbolAddress returns for
+// the device that is current at the time.  It is looked up once per device, on the first call made with that device current -- that
+// first call should therefore happen before any stream capture starts -- and cached.
+// ---------------------------------------------------------------------------------------------------------------------
+namespace wq {
+
+constexpr int64_t kStaticSlotBytes = 2 << 20;     // partial sums: enough for every plan of at most 32 tokens on up to 256 SMs
+constexpr int64_t kStaticCounterBytes = 4 << 10;  // one counter per tile, at most 1024 tiles
+constexpr int64_t kStaticScratchBytes = kStaticSlotBytes + kStaticCounterBytes;
+static __device__ __align__(256) unsigned char static_scratch[kStaticScratchBytes];
+
+// Device address of static_scratch on the current device (nullptr and *error set when the lookup fails).
+static unsigned char* static_scratch_address(int* error) {
+    static unsigned char* known[64] = {};
+    int device = 0;
+    cudaError_t code = cudaGetDevice(&device);
+    if (code != cudaSuccess || device < 0 || device >= 64) {
+        *error = code != cudaSuccess ? int(code) : -2;
+        return nullptr;
+    }
+    if (!known[device]) {
+        void* address = nullptr;
+        code = cudaGetSymbolAddress(&address, static_scratch);
+        if (code != cudaSuccess || !address) {
+            *error = code != cudaSuccess ? int(code) : int(cudaErrorInvalidSymbol);
+            return nullptr;
+        }
+        known[device] = static_cast<unsigned char*>(address);
+    }
+    return known[device];
+}
+
+}  // namespace wq
+
+// Same linear as wq8_small (at most 32 tokens, K multiple of 64, x rows 16-byte aligned), same values, no scratch arguments and no
+// allocation of any kind: the K-split partial sums and tile counters use the library's own static device buffer.
+// Returns -5 when the shape's scratch would not fit that buffer (use wq8_small with caller scratch then); other codes as wq8_small.
+// Calls share the one buffer per device: two calls whose kernels may overlap on the GPU (different streams, or one stream of a graph with
+// parallel branches) race on it -- keep them on one stream, or give the others caller scratch through wq8_small.  The buffer keeps what
+// the last call left in it; the counters are cleared on the stream in front of every launch, the slots are written before they are read.
+WQ_API int wq8_small_static(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
+                            void* y, int m, int n, int k, int dtype, int sms, cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (k <= 0 || k % 64 || m > 32 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return -2;
+    if (dtype != 0 && dtype != 1) return -1;
+    const StreamPlan p = plan_stream(n, k, sms, true);
+    float* slots = nullptr;
+    int* counters = nullptr;
+    if (p.splits > 1) {
+        const int64_t outputs = int64_t(8 / p.wk) * tokens_blocks(m) * 8 * 16;
+        const int64_t slot_bytes = int64_t(p.ctas) * p.splits * outputs * 4, counter_bytes = 4 * int64_t(p.ctas);
+        if (slot_bytes > kStaticSlotBytes || counter_bytes > kStaticCounterBytes) return -5;
+        int error = 0;
+        unsigned char* scratch = static_scratch_address(&error);
+        if (!scratch) return error;
+        slots = reinterpret_cast<float*>(scratch);
+        counters = reinterpret_cast<int*>(scratch + kStaticSlotBytes);
+        const cudaError_t cleared = cudaMemsetAsync(counters, 0, size_t(counter_bytes), stream);
+        if (cleared != cudaSuccess) return int(cleared);
+    }
+    if (dtype == 0) return launch_stream<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, slots, counters, stream);
+    return launch_stream<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, slots, counters, stream);
+}
