@@ -31,11 +31,23 @@ constexpr int kStageK = 128;         // bytes (= INT8 elements) of K per stage: 
 constexpr int kMmaK = 32;            // K of one tcgen05.mma kind::i8
 constexpr int kTmemColumns = 512;    // all of an SM's tensor memory (one CTA per SM)
 constexpr int kEpilogueWarps = 8;
-constexpr int kThreads = 32 * (4 + kEpilogueWarps);
+constexpr int kRearmWarps = 4;       // one per lane quarter of tensor memory: they put the conversion bias back into drained accumulators
+constexpr int kThreads = 32 * (4 + kEpilogueWarps + kRearmWarps);
+// Registers per thread after the split (setmaxnreg): 512 threads are launched with 128 each; the control and re-arm warps keep 40 and
+// the epilogue warps, which hold a tile's FP32 accumulators, take 208: 256 x 40 + 256 x 208 = 63488 of the 65536.
+constexpr int kSmallRegs = 40, kEpilogueRegs = 208;
 constexpr int kScaleRing = 4;        // blocks of gathered weight scales in flight
 constexpr long long kWaitLimit = 4000000000ll;  // clocks (about two seconds) before a wait gives up
 
 __device__ int g_status = 0;  // first code of a wait that gave up (wq::Status)
+
+#ifdef WQ_TRACE
+// Diagnostic build only: clock stamps of CTA 0 (MMA issuer at slot 0, first epilogue warp at slot 4096), read back by wq8_debug_trace.
+__device__ long long g_trace[8192];
+#define WQ_STAMP(base, index, field) do { if (blockIdx.x == 0 && (index) < 500) g_trace[(base) + (index) * 8 + (field)] = clock64(); } while (0)
+#else
+#define WQ_STAMP(base, index, field) do {} while (0)
+#endif
 
 // ---- PTX wrappers --------------------------------------------------------------------------------------------------
 WQ_DEVICE uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -60,9 +72,22 @@ WQ_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 
+// Non-blocking test of the phase: the cheap first look (the phase has usually completed by the time a role asks).
+WQ_DEVICE bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
 // Waits for the phase of `parity`; false when the CTA is aborting or the wait ran out (then `code` is recorded and the abort flag raised).
 WQ_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_test(bar, parity)) return true;
     const long long start = clock64();
     for (uint32_t spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -214,13 +239,15 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     float* scale_ring = reinterpret_cast<float*>(smem + kStages * S::kStageBytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes + S::kRingBytes);
-    // barrier layout: full[kStages], empty[kStages], acc_full[2], acc_empty[2], ring_full[kScaleRing], ring_empty[kScaleRing]
+    // barrier layout: full[kStages], empty[kStages], acc_full[2], acc_empty[2], ring_full[kScaleRing], ring_empty[kScaleRing], drained[2]
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * kStages, bar_acc_full = bar_empty + 8 * kStages,
-                   bar_acc_empty = bar_acc_full + 16, bar_ring_full = bar_acc_empty + 16, bar_ring_empty = bar_ring_full + 8 * kScaleRing;
+                   bar_acc_empty = bar_acc_full + 16, bar_ring_full = bar_acc_empty + 16, bar_ring_empty = bar_ring_full + 8 * kScaleRing,
+                   bar_drained = bar_ring_empty + 8 * kScaleRing;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_word;
     volatile int* abort_flag = &abort_word;
 
+    constexpr bool kBiased = S::kFold && FOLD == kFoldBiased && !DUMP;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kblocks = (p.k + kStageK - 1) / kStageK;
     const int tiles = p.tiles_m * p.tiles_n;
@@ -233,10 +260,11 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar_acc_full + 8 * s, 1);
-            mbar_init(bar_acc_empty + 8 * s, kEpilogueWarps);
+            mbar_init(bar_acc_empty + 8 * s, kBiased ? kRearmWarps : kEpilogueWarps);
+            mbar_init(bar_drained + 8 * s, kEpilogueWarps);
         }
         for (int s = 0; s < kScaleRing; ++s) {
-            mbar_init(bar_ring_full + 8 * s, 64);
+            mbar_init(bar_ring_full + 8 * s, 32);
             mbar_init(bar_ring_empty + 8 * s, kEpilogueWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -249,16 +277,13 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
-    constexpr bool kBiased = S::kFold && FOLD == kFoldBiased && !DUMP;
+    int bias_run[16];
     if constexpr (kBiased) {
-        // arm every accumulator column with the bias bits once; from here on each drain re-arms what it read
-        if (warp >= 4) {
-            int bias_run[16];
+        // the re-arm warps put the bias bits into every accumulator column once; from here on they do it after each drain
+        if (warp >= 4 + kEpilogueWarps) {
             load_bias_run(bias_run);
-            const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + ((warp - 4) >> 2) * kEpi;
-            for (int buffer = 0; buffer < kAccBuffers; ++buffer)
-                for (int part = 0; part < (S::kHilo ? 2 : 1); ++part)
-                    for (int chunk = 0; chunk < kEpi / 32; ++chunk) tmem_store_32(lane_addr + buffer * S::kAccColumns + part * BN + chunk * 32, bias_run);
+            const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
+            for (int column = 0; column < kTmemColumns; column += 32) tmem_store_32(lane_addr + column, bias_run);
             tmem_store_wait();
         }
         tc_fence_before();
@@ -266,10 +291,8 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         tc_fence_after();
     }
 
-    // Registers move from the four control warps to the eight epilogue warps, which hold a tile's FP32 accumulators:
-    // 128 x 56 + 256 x 224 = 64512 registers, what 384 threads x 168 were launched with.
     if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kSmallRegs));
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
@@ -298,15 +321,15 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        // ---------------- MMA issuer (modes that accumulate over all of K in one buffer) ----------------
+        if (!S::kFold && lane == 0) {
             constexpr uint32_t idesc = instruction_descriptor(BN);
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    const bool new_acc = S::kFold || kb == 0;
+                    const bool new_acc = kb == 0;
                     if (new_acc && !(ok = mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kTimeoutTmemEmpty))) break;
                     if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, kTimeoutFull))) break;
                     tc_fence_after();
@@ -316,24 +339,59 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     const uint32_t d = tmem_base + acc * S::kAccColumns;
 #pragma unroll
                     for (int j = 0; j < kStageK / kMmaK; ++j) {
-                        const uint32_t accumulate = (!kBiased && new_acc && j == 0) ? 0u : 1u;
+                        const uint32_t accumulate = (new_acc && j == 0) ? 0u : 1u;
                         const uint64_t step = uint64_t(j * kMmaK >> 4);  // start address advances in 16-byte units inside the swizzle row
                         mma_i8(d, a_desc + step, b_desc + step, idesc, accumulate);
                         if (S::kHilo) mma_i8(d + BN, a_lo_desc + step, b_desc + step, idesc, accumulate);
                     }
                     tc_commit(bar_empty + 8 * stage);  // the stage may be refilled once these MMAs have read it
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
-                    if (S::kFold || kb == kblocks - 1) {
+                    if (kb == kblocks - 1) {
                         tc_commit(bar_acc_full + 8 * acc);
                         if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1u; }
                     }
                 }
             }
         }
-    } else if (warp < 4) {
+    }
+    if (S::kFold && (warp == 1 || warp == 2)) {
+        // ---------------- MMA issuers of the per-block modes: two threads, one per accumulator buffer ----------------
+        // Block g goes to buffer g % 2 and is issued by thread g % 2.  One thread alone spends more time per block on its barrier tests
+        // and commits than the four MMAs run; with two, one thread's bookkeeping overlaps the other one's MMAs.
+        if (lane == 0) {
+            static_assert(!S::kFold || (kStages % 2 == 0 && kAccBuffers == 2), "two issuers alternate over an even number of stages");
+            constexpr uint32_t idesc = instruction_descriptor(BN);
+            const int me = warp - 1;
+            const int total = ((tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x)) * kblocks;
+            int stage = me;
+            uint32_t phase = 0, acc_phase = 0;
+            const uint32_t d = tmem_base + me * S::kAccColumns;
+            for (int g = me; g < total; g += 2) {
+                if (!mbar_wait(bar_acc_empty + 8 * me, acc_phase ^ 1u, abort_flag, kTimeoutTmemEmpty)) break;
+                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, kTimeoutFull)) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + stage * S::kStageBytes);
+                const uint64_t a_desc = smem_descriptor(a_addr), a_lo_desc = smem_descriptor(a_addr + S::kABytes),
+                               b_desc = smem_descriptor(a_addr + S::kABytes * (S::kHilo ? 2 : 1));
+#pragma unroll
+                for (int j = 0; j < kStageK / kMmaK; ++j) {
+                    const uint32_t accumulate = (!kBiased && j == 0) ? 0u : 1u;
+                    const uint64_t step = uint64_t(j * kMmaK >> 4);
+                    mma_i8(d, a_desc + step, b_desc + step, idesc, accumulate);
+                    if (S::kHilo) mma_i8(d + BN, a_lo_desc + step, b_desc + step, idesc, accumulate);
+                }
+                tc_commit(bar_empty + 8 * stage);
+                tc_commit(bar_acc_full + 8 * me);
+                stage += 2;
+                if (stage >= kStages) { stage -= kStages; phase ^= 1u; }
+                acc_phase ^= 1u;
+            }
+        }
+    }
+    if (warp == 3) {
         // ---------------- weight-scale gather (group-scaled weights) ----------------
         if constexpr (S::kWGroup) {
-            const int loader = threadIdx.x - 64;  // 0..63
+            const int loader = lane;
             int slot = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -341,7 +399,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                 const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n);
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!(ok = mbar_wait(bar_ring_empty + 8 * slot, phase ^ 1u, abort_flag, kTimeoutScales))) break;
-                    for (int i = loader; i < BN; i += 64) {
+                    for (int i = loader; i < BN; i += 32) {
                         const int col = c.n0 + i;
                         scale_ring[slot * BN + i] = col < p.n ? __ldg(p.sb + int64_t(col) * kblocks + kb) : 0.f;
                     }
@@ -351,9 +409,29 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             }
         }
     }
+    } else if (warp >= 4 + kEpilogueWarps) {
+        // ---------------- re-arm (accumulators that start at the conversion bias) ----------------
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kSmallRegs));
+        if constexpr (kBiased) {
+            const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
+            const long long blocks = (long long)((tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x)) * kblocks;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            for (long long b = 0; b < blocks; ++b) {
+                if (!__all_sync(0xffffffffu, mbar_wait(bar_drained + 8 * acc, acc_phase, abort_flag, kTimeoutTmemEmpty))) break;
+                tc_fence_after();
+#pragma unroll
+                for (int column = 0; column < S::kAccColumns; column += 32) tmem_store_32(lane_addr + acc * S::kAccColumns + column, bias_run);
+                tmem_store_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+                if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
     } else {
         // ---------------- epilogue ----------------
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpilogueRegs));
         const int quarter = warp & 3, half = (warp - 4) >> 2;
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
         const T* bias = static_cast<const T*>(p.bias);
@@ -363,14 +441,22 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         int acc = 0, slot = 0;
         uint32_t acc_phase = 0, ring_phase = 0;
         bool ok = true;
-        int bias_run[16];
-        if constexpr (kBiased) load_bias_run(bias_run);
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
             const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n);
             const int row = c.m0 + quarter * 32 + lane;
             const bool row_ok = row < p.m;
             const int col0 = c.n0 + half * kEpi;
             const float row_scale = S::kBlockScales ? 1.f : (row_ok ? __ldg(p.sa + row) : 0.f);
+            // The column parameters of this thread's part of the tile (weight scales, bias, residual scale) are only needed when the tile
+            // ends; asking for their cache lines now lets the tile epilogue find them in L1 instead of paying an L2 round trip per group.
+            if (p.vector_io && lane < 8) {
+                const char* line = nullptr;
+                if (lane < 4) line = S::kWGroup ? nullptr : reinterpret_cast<const char*>(p.sb + col0) + 128 * lane;
+                else if (lane < 6) line = bias ? reinterpret_cast<const char*>(bias + col0) + 128 * (lane - 4) : nullptr;
+                else line = rscale ? reinterpret_cast<const char*>(rscale + col0) + 128 * (lane - 6) : nullptr;
+                const int first_col = lane < 4 ? col0 + 32 * lane : lane < 6 ? col0 + 64 * (lane - 4) : col0 + 64 * (lane - 6);
+                if (line && first_col < p.n) asm volatile("prefetch.global.L1 [%0];" ::"l"(line));
+            }
 
             // y values of 32 columns starting at `col`: bias, residual, one rounding, store
             auto emit = [&](const float* v, int col) {
@@ -414,7 +500,11 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                         packed.y = pack_pair<T>(out[2], out[3]);
                         packed.z = pack_pair<T>(out[4], out[5]);
                         packed.w = pack_pair<T>(out[6], out[7]);
+#if defined(WQ_DIAG) && WQ_DIAG == 3
+                        if (packed.x == 0x12345678u) *reinterpret_cast<uint4*>(dst + j) = packed;  // diagnostic: (almost) no stores
+#else
                         *reinterpret_cast<uint4*>(dst + j) = packed;
+#endif
                     }
                     return;
                 }
@@ -443,6 +533,14 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     sa_next = row_ok && kblocks > 1 ? __ldg(sa_row + 1) : 0.f;
                 }
                 for (int kb = 0; kb < kblocks; ++kb) {
+#ifdef WQ_TRACE
+                    const int stamp = (t / int(gridDim.x)) * kblocks + kb;
+                    const int tbase = (warp == 4 && lane == 0) ? 4096 : 1 << 30;
+#define WQ_ESTAMP(field) do { if (tbase == 4096) WQ_STAMP(4096, stamp, field); } while (0)
+#else
+#define WQ_ESTAMP(field) do {} while (0)
+#endif
+                    WQ_ESTAMP(0);
                     float sa_after = 0.f;
                     if constexpr (S::kBlockScales && !DUMP) {
                         if (row_ok && kb + 2 < kblocks) sa_after = __ldg(p.sa + int64_t(row) * kblocks + kb + 2);
@@ -451,6 +549,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                         if (!(ok = __all_sync(0xffffffffu, mbar_wait(bar_ring_full + 8 * slot, ring_phase, abort_flag, kTimeoutScales)))) break;
                     }
                     if (!(ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, kTimeoutTmemFull)))) break;
+                    WQ_ESTAMP(1);
                     tc_fence_after();
                     const uint32_t taddr = tmem_base + lane_base + acc * S::kAccColumns + half * kEpi;
                     const float* ring = scale_ring + slot * BN + half * kEpi;
@@ -462,17 +561,12 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                         tmem_load_32(taddr + chunk * 32, hi[chunk & 1]);
                         if (S::kHilo) tmem_load_32(taddr + BN + chunk * 32, lo[chunk & 1]);
                     };
-                    auto rearm = [&](int chunk) {
-                        if constexpr (kBiased) {
-                            tmem_store_32(taddr + chunk * 32, bias_run);
-                            if (S::kHilo) tmem_store_32(taddr + BN + chunk * 32, bias_run);
-                        }
-                    };
                     auto release = [&]() {
-                        if constexpr (kBiased) tmem_store_wait();
+                        // every column of this warp's part of the buffer has been read: it goes back to the MMAs, through the re-arm warps
+                        // when the accumulators have to start at the conversion bias again
                         tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+                        if (lane == 0) mbar_arrive((kBiased ? bar_drained : bar_acc_empty) + 8 * acc);
                     };
                     auto fold = [&](int chunk) {
                         const int* h = hi[chunk & 1];
@@ -483,16 +577,37 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                                 for (int j = 0; j < 32; ++j)
                                     if (col0 + chunk * 32 + j < p.n) p.dump[(int64_t(kb) * p.m + row) * p.n + col0 + chunk * 32 + j] = h[j];
                         } else {
+                            // three passes over the chunk, each of 32 independent instructions, converting in place: the dependent
+                            // add -> subtract -> multiply-add of one element are never issued back to back
+                            float v[32];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = __int_as_float(FOLD == kFoldAdd ? h[j] + kBiasBits : h[j]);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] -= kBiasValue;
+                            if constexpr (MODE == kExactG) {
+                                float w[32];
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) w[j] = __int_as_float(FOLD == kFoldAdd ? l[j] + kBiasBits : l[j]);
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) w[j] -= kBiasValue;
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) v[j] = fmaf(w[j], 1.f / 254.f, v[j]);
+                            }
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
                                 float* a = &accf[chunk * 32 + j];
-                                const float v = block_sum_to_float<FOLD>(h[j]);
                                 if constexpr (MODE == kBlock) {
-                                    *a = fmaf(v, sa_now, *a);
+#if defined(WQ_DIAG) && WQ_DIAG == 1
+                                    *a = v[j];  // diagnostic: conversion only
+#elif defined(WQ_DIAG) && WQ_DIAG == 2
+                                    *a = fmaf(__int_as_float(h[j]), sa_now, *a);  // diagnostic: one FMA on the raw bits, no conversion
+#else
+                                    *a = fmaf(v[j], sa_now, *a);
+#endif
                                 } else if constexpr (MODE == kBlockG) {
-                                    *a = fmaf(v, sa_now * ring[chunk * 32 + j], *a);
+                                    *a = fmaf(v[j], sa_now * ring[chunk * 32 + j], *a);
                                 } else {
-                                    *a = fmaf(fmaf(block_sum_to_float<FOLD>(l[j]), 1.f / 254.f, v), ring[chunk * 32 + j], *a);
+                                    *a = fmaf(v[j], ring[chunk * 32 + j], *a);
                                 }
                             }
                         }
@@ -501,8 +616,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     fetch(0);
                     fetch(1);
                     tmem_load_wait();
-                    rearm(0);
-                    rearm(1);
+                    WQ_ESTAMP(2);
                     if (kChunks == 2) release();
 #pragma unroll
                     for (int chunk = 0; chunk < kChunks; ++chunk) {
@@ -511,9 +625,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                             fetch(chunk + 2);  // into the staging buffer just folded
                             if (chunk & 1) {   // chunks chunk + 1 and chunk + 2 are in flight: complete the pair
                                 tmem_load_wait();
-                                rearm(chunk + 1);
-                                rearm(chunk + 2);
-                                if (chunk + 2 == kChunks - 1) release();
+                                if (chunk + 2 == kChunks - 1) { WQ_ESTAMP(3); release(); WQ_ESTAMP(4); }
                             }
                         }
                     }
@@ -521,6 +633,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                         __syncwarp();
                         if (lane == 0) mbar_arrive(bar_ring_empty + 8 * slot);
                     }
+                    WQ_ESTAMP(5);
                     if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1u; }
                     if (S::kWGroup && ++slot == kScaleRing) { slot = 0; ring_phase ^= 1u; }
                     sa_now = sa_next;
@@ -781,6 +894,13 @@ WQ_API int wq8_debug_mma_peak(int kind, int iters, int sms, double* results) {
     results[2] = cycles / (iters < 0 ? -iters : iters);
     return 0;
 }
+
+#ifdef WQ_TRACE
+WQ_API int wq8_debug_trace(long long* host_out) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    return int(cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 8192));
+}
+#endif
 
 WQ_API int wq8_debug_status() {
     int code = 0;

@@ -15,9 +15,14 @@ WQ_DEVICE void store_chunk_as_blocks(const float* v, int lane, int64_t row, int 
     for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
 #pragma unroll
     for (int d = 8; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));  // stays inside each half warp
-    const float inv = amax > 0.f ? 127.f / amax : 0.f;
-    const int block = base / kBlockK + (lane >> 4);
-    if ((lane & 15) == 0 && block < kblocks) scale[row * kblocks + block] = amax * group_norm<GROUP>() / 127.f;
+    // the two IEEE divisions of a block are done by its first lane only; the other fifteen receive the reciprocal scale
+    float inv = 0.f;
+    if ((lane & 15) == 0) {
+        inv = amax > 0.f ? 127.f / amax : 0.f;
+        const int block = base / kBlockK + (lane >> 4);
+        if (block < kblocks) scale[row * kblocks + block] = amax * group_norm<GROUP>() / 127.f;
+    }
+    inv = __shfl_sync(0xffffffffu, inv, lane & 16);
     const int col = base + lane * 8;
     if (col < k) {
         int c[8];
@@ -27,19 +32,27 @@ WQ_DEVICE void store_chunk_as_blocks(const float* v, int lane, int64_t row, int 
     }
 }
 
-// Blocks are independent when no row statistic is needed: a warp per 256-element chunk, persistent warps striding over all
-// (row, chunk) items with two items in flight per warp.
+// Blocks are independent when no row statistic is needed: a warp per 256-element chunk, persistent warps, two chunks in flight per warp.
 template <class T, int GROUP, int ACT>
 __global__ void __launch_bounds__(256) quantize_blocks_stream(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, int m,
                                                               int k, int64_t ldx) {
     const int lane = threadIdx.x & 31;
     const int chunks = (k + kChunk - 1) / kChunk, kblocks = (k + kBlockK - 1) / kBlockK;
-    const int64_t items = int64_t(m) * chunks, stride = int64_t(gridDim.x) * 8;
-    for (int64_t item = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5); item < items; item += 2 * stride) {
-        const int64_t second = item + stride;
-        const bool pair = second < items;
-        const int64_t row0 = item / chunks, row1 = pair ? second / chunks : row0;
-        const int base0 = int(item % chunks) * kChunk, base1 = pair ? int(second % chunks) * kChunk : base0;
+    const int64_t items = int64_t(m) * chunks, warps = int64_t(gridDim.x) * 8, warp_id = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    // each warp takes a contiguous run of (row, chunk) items: one division up front, then the chunk index just advances
+    const int64_t per_warp = (items + warps - 1) / warps, first = warp_id * per_warp;
+    const int64_t last = first + per_warp < items ? first + per_warp : items;
+    if (first >= last) return;
+    int64_t row = first / chunks;
+    int chunk = int(first - row * chunks);
+    for (int64_t item = first; item < last; item += 2) {
+        const bool pair = item + 1 < last;
+        const int64_t row0 = row;
+        const int base0 = chunk * kChunk;
+        if (++chunk == chunks) { chunk = 0; ++row; }
+        const int64_t row1 = row;
+        const int base1 = chunk * kChunk;
+        if (pair && ++chunk == chunks) { chunk = 0; ++row; }
         float v0[8], v1[8];
         load_op<T, ACT>(x + row0 * ldx, k, base0 + lane * 8, v0, base0 + lane * 8 < k);
         load_op<T, ACT>(x + row1 * ldx, k, base1 + lane * 8, v1, pair && base1 + lane * 8 < k);
@@ -56,7 +69,7 @@ __global__ void __launch_bounds__(256) quantize_blocks_stream(const T* __restric
 // CPW == 0: any K, the row is read twice (the second read comes from L2).
 // Sum of squares: thread (warp w, lane l) accumulates fmaf(v, v, ss) over chunks w, w + 8, ... in order; then the ordered CTA sum.
 template <class T, int GROUP, int CPW>
-__global__ void __launch_bounds__(kRowThreads) quantize_blocks_rms(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, int k,
+__global__ void __launch_bounds__(kRowThreads) quantize_blocks_rms(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, int m, int k,
                                                                    int64_t ldx, const T* __restrict__ act_weight, float eps) {
     __shared__ float slots[8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -65,20 +78,33 @@ __global__ void __launch_bounds__(kRowThreads) quantize_blocks_rms(const T* __re
     const int kblocks = (k + kBlockK - 1) / kBlockK;
     float ss = 0.f;
     if constexpr (CPW > 0) {
+        // The row and this thread's slice of the RMSNorm weight are requested together, before the reduction: nothing is loaded
+        // between the barrier and the stores.
+        static_assert(sizeof(T) == 2, "rms_norm takes 16-bit inputs");
         float v[CPW][8];
+        uint4 weight_raw[CPW];
 #pragma unroll
         for (int i = 0; i < CPW; ++i) {
             const int col = (warp + 8 * i) * kChunk + lane * 8;
             load_eight(src + col, v[i], col < k);
+            weight_raw[i] = (act_weight && col < k) ? __ldg(reinterpret_cast<const uint4*>(act_weight + col)) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int i = 0; i < CPW; ++i)
 #pragma unroll
             for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
-        }
         const float inv_rms = inverse_rms(cta_sum_ordered(ss, slots), k, eps);
 #pragma unroll
         for (int i = 0; i < CPW; ++i) {
             const int base = (warp + 8 * i) * kChunk;
             if (base < k) {  // warp-uniform
-                scale_by_rms(v[i], inv_rms, act_weight, base + lane * 8, base + lane * 8 < k);
+                float w[8];
+                unpack_pair<T>(weight_raw[i].x, w[0], w[1]);
+                unpack_pair<T>(weight_raw[i].y, w[2], w[3]);
+                unpack_pair<T>(weight_raw[i].z, w[4], w[5]);
+                unpack_pair<T>(weight_raw[i].w, w[6], w[7]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[i][j] = v[i][j] * inv_rms * (act_weight ? w[j] : 1.f);
                 rotate_chunk<GROUP>(v[i]);
                 store_chunk_as_blocks<GROUP>(v[i], lane, row, base, k, kblocks, q, scale);
             }
@@ -262,16 +288,24 @@ static int persistent_ctas(int64_t warps_of_work) {
     return int(ctas < cap ? (ctas < 1 ? 1 : ctas) : cap);
 }
 
+// CTAs of the persistent one-row-at-a-time kernels: every row its own CTA up to eight resident CTAs per SM.
+static int row_ctas(int m) {
+    int device = 0, sms = 148;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    return m < sms * 8 ? m : sms * 8;
+}
+
 template <class T, int GROUP, int ACT>
 static int launch_blocks(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, const void* act_weight, float eps, cudaStream_t stream) {
     auto src = static_cast<const T*>(x);
     auto aw = static_cast<const T*>(act_weight);
     if constexpr (ACT == kActRms) {
-        if (k <= 2048) quantize_blocks_rms<T, GROUP, 1><<<m, kRowThreads, 0, stream>>>(src, q, scale, k, ldx, aw, eps);
-        else if (k <= 4096) quantize_blocks_rms<T, GROUP, 2><<<m, kRowThreads, 0, stream>>>(src, q, scale, k, ldx, aw, eps);
-        else if (k <= 8192) quantize_blocks_rms<T, GROUP, 4><<<m, kRowThreads, 0, stream>>>(src, q, scale, k, ldx, aw, eps);
-        else if (k <= 16384) quantize_blocks_rms<T, GROUP, 8><<<m, kRowThreads, 0, stream>>>(src, q, scale, k, ldx, aw, eps);
-        else quantize_blocks_rms<T, GROUP, 0><<<m, kRowThreads, 0, stream>>>(src, q, scale, k, ldx, aw, eps);
+        if (k <= 2048) quantize_blocks_rms<T, GROUP, 1><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps);
+        else if (k <= 4096) quantize_blocks_rms<T, GROUP, 2><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps);
+        else if (k <= 8192) quantize_blocks_rms<T, GROUP, 4><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps);
+        else if (k <= 16384) quantize_blocks_rms<T, GROUP, 8><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps);
+        else quantize_blocks_rms<T, GROUP, 0><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps);
     } else {
         const int64_t items = int64_t(m) * ((k + kChunk - 1) / kChunk);
         quantize_blocks_stream<T, GROUP, ACT><<<persistent_ctas((items + 1) / 2), 256, 0, stream>>>(src, q, scale, m, k, ldx);
