@@ -41,6 +41,11 @@ constexpr long long kWaitLimit = 4000000000ll;  // clocks (about two seconds) be
 
 __device__ int g_status = 0;  // first code of a wait that gave up (wq::Status)
 
+#ifdef WQ_DIAG
+#define WQ_DIAG_VALUE WQ_DIAG
+#else
+#define WQ_DIAG_VALUE 0
+#endif
 #ifdef WQ_TRACE
 // Diagnostic build only: clock stamps of CTA 0 (MMA issuer at slot 0, first epilogue warp at slot 4096), read back by wq8_debug_trace.
 __device__ long long g_trace[8192];
@@ -203,7 +208,13 @@ template <int MODE, int BN> struct Shape {
     static constexpr int kStages = (196 * 1024) / kStageBytes;
     static constexpr int kEpiColumns = BN / 2;  // columns per epilogue thread (two warpgroups split the tile's columns)
     static constexpr int kRingBytes = kWGroup ? kScaleRing * BN * 4 : 0;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kRingBytes + 1024 /* alignment */ + 256 /* barriers */;
+    // Output staging: every epilogue warp owns kStoreBuffers buffers of 32 rows x 32 columns of 16-bit outputs (2 KiB each, 64-byte
+    // swizzle) from which the TMA unit writes whole 64-byte row segments; two buffers per warp when shared memory has room for them.
+    static constexpr int kStoreTile = 32 * 32 * 2;
+    static constexpr int kFixedBytes = kStages * kStageBytes + kRingBytes + 1024 /* alignment */ + 256 /* barriers */;
+    static constexpr int kStoreBuffers = kFixedBytes + kEpilogueWarps * 2 * kStoreTile <= 227 * 1024 ? 2 : 1;
+    static constexpr int kStoreBytes = kEpilogueWarps * kStoreBuffers * kStoreTile;
+    static constexpr int kSmemBytes = kFixedBytes + kStoreBytes;
     static_assert(kAccBuffers >= 1 && kStages >= 2, "tile does not fit");
 };
 
@@ -218,6 +229,7 @@ struct GemmParams {
     int m, n, k;
     int tiles_m, tiles_n;
     int vector_io;  // y, residual, sb, bias and rscale allow 16-byte accesses (N multiple of 8, aligned bases)
+    int tma_y;      // map_y describes y: whole 32-column chunks leave through shared memory and the TMA unit
 };
 
 struct TileCoord { int m0, n0; };
@@ -232,13 +244,14 @@ template <int BN> WQ_DEVICE TileCoord tile_origin(int t, int tiles_m, int tiles_
 template <class T, int MODE, int BN, int FOLD, bool DUMP>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b,
-           const GemmParams p) {
+           const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
     using S = Shape<MODE, BN>;
     constexpr int kStages = S::kStages, kAccBuffers = S::kAccBuffers, kEpi = S::kEpiColumns;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     float* scale_ring = reinterpret_cast<float*>(smem + kStages * S::kStageBytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes + S::kRingBytes);
+    const uint32_t store_stage = smem_u32(smem + kStages * S::kStageBytes + S::kRingBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes + S::kRingBytes + S::kStoreBytes);
     // barrier layout: full[kStages], empty[kStages], acc_full[2], acc_empty[2], ring_full[kScaleRing], ring_empty[kScaleRing], drained[2]
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * kStages, bar_acc_full = bar_empty + 8 * kStages,
                    bar_acc_empty = bar_acc_full + 16, bar_ring_full = bar_acc_empty + 16, bar_ring_empty = bar_ring_full + 8 * kScaleRing,
@@ -271,6 +284,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
         if (S::kHilo) prefetch_tensormap(&map_a_lo);
+        if (p.tma_y) prefetch_tensormap(&map_y);
     }
     if (warp == 2) tmem_alloc(smem_u32(&tmem_slot), kTmemColumns);
     tc_fence_before();
@@ -438,9 +452,12 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         const T* residual = static_cast<const T*>(p.residual);
         const T* rscale = static_cast<const T*>(p.rscale);
         T* y = static_cast<T*>(p.y);
-        int acc = 0, slot = 0;
+        int acc = 0, slot = 0, store_buffer = 0;
         uint32_t acc_phase = 0, ring_phase = 0;
         bool ok = true;
+        const uint32_t my_stage = store_stage + (warp - 4) * S::kStoreBuffers * S::kStoreTile;
+        float sa_ahead[2] = {0.f, 0.f};
+        bool sa_ahead_valid = false;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
             const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n);
             const int row = c.m0 + quarter * 32 + lane;
@@ -460,15 +477,24 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
 
             // y values of 32 columns starting at `col`: bias, residual, one rounding, store
             auto emit = [&](const float* v, int col) {
-                if (!row_ok || col >= p.n) return;
+                if (col >= p.n) return;
+                const bool staged = p.tma_y && col + 32 <= p.n;  // the same for the whole warp
+                if (!row_ok && !staged) return;
                 T* dst = y + int64_t(row) * p.n + col;
-                const T* res = residual ? residual + int64_t(row) * p.n + col : nullptr;
+                const T* res = residual && row_ok ? residual + int64_t(row) * p.n + col : nullptr;
+                uint32_t stage_row = 0;
+                if (staged) {
+                    // the TMA store that last read this buffer must be done with it before the warp writes it again
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(S::kStoreBuffers - 1) : "memory");
+                    __syncwarp();
+                    stage_row = my_stage + store_buffer * S::kStoreTile + lane * 64;
+                }
                 if (p.vector_io && col + 32 <= p.n) {
                     // whole chunk, every operand 16-byte aligned: eight outputs per step with 128-bit accesses
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
                         float scale8[8], bias8[8], out[8];
-                        if constexpr (S::kWGroup) {
+                        if constexpr (S::kWGroup || WQ_DIAG_VALUE == 4) {
 #pragma unroll
                             for (int e = 0; e < 8; ++e) scale8[e] = 1.f;
                         } else {
@@ -500,11 +526,26 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                         packed.y = pack_pair<T>(out[2], out[3]);
                         packed.z = pack_pair<T>(out[4], out[5]);
                         packed.w = pack_pair<T>(out[6], out[7]);
-#if defined(WQ_DIAG) && WQ_DIAG == 3
-                        if (packed.x == 0x12345678u) *reinterpret_cast<uint4*>(dst + j) = packed;  // diagnostic: (almost) no stores
-#else
-                        *reinterpret_cast<uint4*>(dst + j) = packed;
-#endif
+                        if (staged) {
+                            // row `lane` of the staging tile, 16-byte piece j / 8 at its place in the 64-byte swizzle
+                            const uint32_t piece = uint32_t(j >> 3) ^ ((uint32_t(lane) >> 1) & 3u);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + piece * 16), "r"(packed.x), "r"(packed.y),
+                                         "r"(packed.z), "r"(packed.w)
+                                         : "memory");
+                        } else {
+                            *reinterpret_cast<uint4*>(dst + j) = packed;
+                        }
+                    }
+                    if (staged) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) {
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_y), "r"(col),
+                                         "r"(c.m0 + quarter * 32), "r"(my_stage + store_buffer * S::kStoreTile)
+                                         : "memory");
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
+                        if (++store_buffer == S::kStoreBuffers) store_buffer = 0;
                     }
                     return;
                 }
@@ -528,9 +569,14 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                 // activation block scales: two blocks ahead in registers
                 float sa_now = 0.f, sa_next = 0.f;
                 if constexpr (S::kBlockScales && !DUMP) {
-                    const float* sa_row = p.sa + int64_t(row_ok ? row : 0) * kblocks;
-                    sa_now = row_ok ? __ldg(sa_row) : 0.f;
-                    sa_next = row_ok && kblocks > 1 ? __ldg(sa_row + 1) : 0.f;
+                    if (sa_ahead_valid) {  // requested while the previous tile was being written out
+                        sa_now = sa_ahead[0];
+                        sa_next = sa_ahead[1];
+                    } else {
+                        const float* sa_row = p.sa + int64_t(row_ok ? row : 0) * kblocks;
+                        sa_now = row_ok ? __ldg(sa_row) : 0.f;
+                        sa_next = row_ok && kblocks > 1 ? __ldg(sa_row + 1) : 0.f;
+                    }
                 }
                 for (int kb = 0; kb < kblocks; ++kb) {
 #ifdef WQ_TRACE
@@ -640,10 +686,34 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     sa_next = sa_after;
                 }
                 if (!ok) break;
+                if constexpr (S::kBlockScales && !DUMP) {
+                    // the first two block scales of this thread's row in the next tile: in flight while this tile is written out
+                    const int t_next = t + int(gridDim.x);
+                    sa_ahead_valid = t_next < tiles;
+                    if (sa_ahead_valid) {
+                        const int row_next = tile_origin<BN>(t_next, p.tiles_m, p.tiles_n).m0 + quarter * 32 + lane;
+                        const float* sa_row = p.sa + int64_t(row_next < p.m ? row_next : 0) * kblocks;
+                        sa_ahead[0] = row_next < p.m ? __ldg(sa_row) : 0.f;
+                        sa_ahead[1] = row_next < p.m && kblocks > 1 ? __ldg(sa_row + 1) : 0.f;
+                    }
+                }
+#ifdef WQ_TRACE
+                if (warp == 4 && lane == 0) WQ_STAMP(4096, (t / int(gridDim.x)) * kblocks + kblocks - 1, 6);
+#endif
                 if constexpr (!DUMP) {
+#if WQ_DIAG_VALUE == 5
+                    float total = 0.f;  // diagnostic: no tile epilogue at all
+#pragma unroll
+                    for (int j = 0; j < kEpi; ++j) total += accf[j];
+                    if (total == 123.456f) y[row] = round_one<T>(total);
+#else
 #pragma unroll
                     for (int chunk = 0; chunk < kEpi / 32; ++chunk) emit(&accf[chunk * 32], col0 + chunk * 32);
+#endif
                 }
+#ifdef WQ_TRACE
+                if (warp == 4 && lane == 0) WQ_STAMP(4096, (t / int(gridDim.x)) * kblocks + kblocks - 1, 7);
+#endif
             } else {
                 if (!(ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, kTimeoutTmemFull)))) break;
                 tc_fence_after();
@@ -674,6 +744,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     }
 
     // common exit: every role falls through to here, aborting or not
+    if (warp >= 4 && warp < 4 + kEpilogueWarps && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staged outputs
     tc_fence_before();
     __syncthreads();
     if (warp == 2) {
@@ -775,6 +846,19 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int k, int bo
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// (m, n) row-major matrix of 16-bit outputs -> tensor map with boxes of 32 rows x 32 columns, 64-byte swizzle (stores clip at the edges).
+static bool make_output_map(CUtensorMap* map, const void* base, int m, int n, bool is_bf16) {
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {cuuint64_t(n), cuuint64_t(m)};
+    const cuuint64_t strides[1] = {cuuint64_t(n) * 2};
+    const cuuint32_t box[2] = {32, 32};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                  elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 struct GemmArgs {
     const int8_t* a;
     const int8_t* a_lo;
@@ -803,7 +887,7 @@ static int launch(const GemmArgs& g, cudaStream_t stream) {
     }
     if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15) || (g.a_lo && (reinterpret_cast<uintptr_t>(g.a_lo) & 15)))
         return -2;
-    CUtensorMap map_a, map_a_lo, map_b;
+    CUtensorMap map_a, map_a_lo, map_b, map_y;
     if (!make_map(&map_a, g.a, g.m, g.k, kBM) || !make_map(&map_b, g.b, g.n, g.k, BN)) return int(cudaErrorNotSupported);
     if (S::kHilo) {
         if (!make_map(&map_a_lo, g.a_lo, g.m, g.k, kBM)) return int(cudaErrorNotSupported);
@@ -818,10 +902,12 @@ static int launch(const GemmArgs& g, cudaStream_t stream) {
     const uintptr_t bases = reinterpret_cast<uintptr_t>(g.y) | reinterpret_cast<uintptr_t>(g.residual) | reinterpret_cast<uintptr_t>(g.bias) |
                             reinterpret_cast<uintptr_t>(g.rscale) | (S::kWGroup ? 0 : reinterpret_cast<uintptr_t>(g.sb));
     p.vector_io = g.n % 8 == 0 && (bases & 15) == 0;
+    p.tma_y = !DUMP && p.vector_io && make_output_map(&map_y, g.y, g.m, g.n, std::is_same<T, bf16>::value);
+    if (!p.tma_y) map_y = map_a;
     const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
     const int sms = g.sms > 0 ? g.sms : 148;
     const int grid = int(tiles < sms ? tiles : sms);
-    kernel<<<grid, kThreads, S::kSmemBytes, stream>>>(map_a, map_a_lo, map_b, p);
+    kernel<<<grid, kThreads, S::kSmemBytes, stream>>>(map_a, map_a_lo, map_b, map_y, p);
     return int(cudaGetLastError());
 }
 
