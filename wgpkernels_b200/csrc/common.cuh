@@ -69,6 +69,17 @@ template <class T> WQ_DEVICE void load_eight(const T* p, float* v, bool valid) {
     }
 }
 
+// Eight consecutive 16-bit elements at p (16-byte aligned) as floats, through an ordinary (coherent) load: for data the same
+// kernel writes later.
+template <class T> WQ_DEVICE void load_eight_plain(const T* p, float* v) {
+    static_assert(sizeof(T) == 2, "16-bit element types only");
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    unpack_pair<T>(raw.x, v[0], v[1]);
+    unpack_pair<T>(raw.y, v[2], v[3]);
+    unpack_pair<T>(raw.z, v[4], v[5]);
+    unpack_pair<T>(raw.w, v[6], v[7]);
+}
+
 WQ_DEVICE uint32_t pack_bytes(int a, int b, int c, int d) {
     return (uint32_t(a) & 0xffu) | ((uint32_t(b) & 0xffu) << 8) | ((uint32_t(c) & 0xffu) << 16) | (uint32_t(d) << 24);
 }
@@ -181,6 +192,6 @@ template <int GROUP> WQ_DEVICE void rotate_chunk(float* v) {
 template <int GROUP> __host__ __device__ constexpr float group_norm() { return GROUP == 256 ? 0.0625f : GROUP == 64 ? 0.125f : GROUP == 16 ? 0.25f : 1.f; }
 
 // ---- device status word (bounded waits report here instead of trapping) ----------------------------------------------
-enum Status : int { kOk = 0, kTimeoutFull = 1, kTimeoutEmpty = 2, kTimeoutTmemFull = 3, kTimeoutTmemEmpty = 4, kTimeoutScales = 5 };
+enum Status : int { kOk = 0, kTimeoutFull = 1, kTimeoutEmpty = 2, kTimeoutTmemFull = 3, kTimeoutTmemEmpty = 4, kTimeoutScales = 5, kTimeoutParams = 6, kStatusSharedAlignment = 7 };
 
 }  // namespace wq

@@ -41,11 +41,6 @@ constexpr long long kWaitLimit = 4000000000ll;  // clocks (about two seconds) be
 
 __device__ int g_status = 0;  // first code of a wait that gave up (wq::Status)
 
-#ifdef WQ_DIAG
-#define WQ_DIAG_VALUE WQ_DIAG
-#else
-#define WQ_DIAG_VALUE 0
-#endif
 #ifdef WQ_TRACE
 // Diagnostic build only: clock stamps of CTA 0 (MMA issuer at slot 0, first epilogue warp at slot 4096), read back by wq8_debug_trace.
 __device__ long long g_trace[8192];
@@ -211,7 +206,9 @@ template <int MODE, int BN> struct Shape {
     // Output staging: every epilogue warp owns kStoreBuffers buffers of 32 rows x 32 columns of 16-bit outputs (2 KiB each, 64-byte
     // swizzle) from which the TMA unit writes whole 64-byte row segments; two buffers per warp when shared memory has room for them.
     static constexpr int kStoreTile = 32 * 32 * 2;
-    static constexpr int kFixedBytes = kStages * kStageBytes + kRingBytes + 1024 /* alignment */ + 256 /* barriers */;
+    // Column parameters of the tile being finished (weight scale as FP32, bias and residual scale in the output type), shared by the epilogue warps.
+    static constexpr int kParamBytes = BN * 8;
+    static constexpr int kFixedBytes = kStages * kStageBytes + kRingBytes + kParamBytes + 256 /* barriers, TMEM slot, abort flag */;
     static constexpr int kStoreBuffers = kFixedBytes + kEpilogueWarps * 2 * kStoreTile <= 227 * 1024 ? 2 : 1;
     static constexpr int kStoreBytes = kEpilogueWarps * kStoreBuffers * kStoreTile;
     static constexpr int kSmemBytes = kFixedBytes + kStoreBytes;
@@ -247,17 +244,29 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
            const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
     using S = Shape<MODE, BN>;
     constexpr int kStages = S::kStages, kAccBuffers = S::kAccBuffers, kEpi = S::kEpiColumns;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // No static shared memory in this kernel: the dynamic block starts at the CTA's shared window, which is 1024-byte aligned (the
+    // 128-byte swizzle of the operand stages needs that); a launch that finds it otherwise reports it and does nothing.
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if (smem_u32(smem) & 1023u) {
+        if (threadIdx.x == 0) atomicCAS(&g_status, 0, int(kStatusSharedAlignment));
+        return;
+    }
     float* scale_ring = reinterpret_cast<float*>(smem + kStages * S::kStageBytes);
     const uint32_t store_stage = smem_u32(smem + kStages * S::kStageBytes + S::kRingBytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes + S::kRingBytes + S::kStoreBytes);
-    // barrier layout: full[kStages], empty[kStages], acc_full[2], acc_empty[2], ring_full[kScaleRing], ring_empty[kScaleRing], drained[2]
+    float* store_stage_generic = reinterpret_cast<float*>(smem + kStages * S::kStageBytes + S::kRingBytes);
+    uint8_t* params = smem + kStages * S::kStageBytes + S::kRingBytes + S::kStoreBytes;
+    float* param_sb = reinterpret_cast<float*>(params);
+    T* param_bias = reinterpret_cast<T*>(params + BN * 4);
+    T* param_rscale = reinterpret_cast<T*>(params + BN * 6);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(params + S::kParamBytes);
+    // barrier layout: full[kStages], empty[kStages], acc_full[2], acc_empty[2], ring_full[kScaleRing], ring_empty[kScaleRing], drained[2],
+    // params_written, params_consumed; then the TMEM slot and the abort flag
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * kStages, bar_acc_full = bar_empty + 8 * kStages,
                    bar_acc_empty = bar_acc_full + 16, bar_ring_full = bar_acc_empty + 16, bar_ring_empty = bar_ring_full + 8 * kScaleRing,
-                   bar_drained = bar_ring_empty + 8 * kScaleRing;
-    __shared__ uint32_t tmem_slot;
-    __shared__ int abort_word;
+                   bar_drained = bar_ring_empty + 8 * kScaleRing, bar_params_written = bar_drained + 16, bar_params_consumed = bar_params_written + 8;
+    static_assert(8 * (2 * kStages + 2 + 2 + 2 * kScaleRing + 2 + 2) <= 224, "barriers overlap the TMEM slot");
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(bars) + 224);
+    int& abort_word = *reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 228);
     volatile int* abort_flag = &abort_word;
 
     constexpr bool kBiased = S::kFold && FOLD == kFoldBiased && !DUMP;
@@ -276,6 +285,8 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             mbar_init(bar_acc_empty + 8 * s, kBiased ? kRearmWarps : kEpilogueWarps);
             mbar_init(bar_drained + 8 * s, kEpilogueWarps);
         }
+        mbar_init(bar_params_written, 32);
+        mbar_init(bar_params_consumed, kEpilogueWarps);
         for (int s = 0; s < kScaleRing; ++s) {
             mbar_init(bar_ring_full + 8 * s, 32);
             mbar_init(bar_ring_empty + 8 * s, kEpilogueWarps);
@@ -403,22 +414,48 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         }
     }
     if (warp == 3) {
-        // ---------------- weight-scale gather (group-scaled weights) ----------------
-        if constexpr (S::kWGroup) {
-            const int loader = lane;
-            int slot = 0;
+        // ---------------- column parameters: per tile for the write-out, per block for group-scaled weights ----------------
+        // The write-out of a tile needs each column's weight scale, bias and residual scale.  Fetching them there would put a trip to
+        // L2 (long, while the operand loads keep it busy) in front of every group of outputs; this warp puts them into shared memory
+        // one tile ahead instead: as FP32 weight scale, bias (0 if none) and residual scale (1 if none) in the output type.
+        if constexpr (!DUMP) {
+            const T* bias = static_cast<const T*>(p.bias);
+            const T* rscale = static_cast<const T*>(p.rscale);
+            int slot = 0, tile_count = 0;
             uint32_t phase = 0;
             bool ok = true;
+            auto stage_params = [&](const TileCoord& c) -> bool {
+                if (!p.vector_io) return true;
+                // every epilogue warp is done with the previous tile's parameters
+                if (tile_count > 0 && !mbar_wait(bar_params_consumed, uint32_t(tile_count - 1) & 1u, abort_flag, kTimeoutParams)) return false;
+                for (int i = lane; i < BN; i += 32) {
+                    const int col = c.n0 + i;
+                    const bool inside = col < p.n;
+                    param_sb[i] = !S::kWGroup && inside ? __ldg(p.sb + col) : 0.f;
+                    param_bias[i] = bias && inside ? bias[col] : round_one<T>(0.f);
+                    param_rscale[i] = rscale && inside ? rscale[col] : round_one<T>(1.f);
+                }
+                mbar_arrive(bar_params_written);
+                ++tile_count;
+                return true;
+            };
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
                 const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n);
-                for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!(ok = mbar_wait(bar_ring_empty + 8 * slot, phase ^ 1u, abort_flag, kTimeoutScales))) break;
-                    for (int i = loader; i < BN; i += 32) {
-                        const int col = c.n0 + i;
-                        scale_ring[slot * BN + i] = col < p.n ? __ldg(p.sb + int64_t(col) * kblocks + kb) : 0.f;
+                if constexpr (S::kWGroup) {
+                    // the first two blocks' scales go first: the epilogue warps start on them right after the previous tile's write-out
+                    const int params_after = (kblocks < 2 ? kblocks : 2) - 1;
+                    for (int kb = 0; kb < kblocks && ok; ++kb) {
+                        if (!(ok = mbar_wait(bar_ring_empty + 8 * slot, phase ^ 1u, abort_flag, kTimeoutScales))) break;
+                        for (int i = lane; i < BN; i += 32) {
+                            const int col = c.n0 + i;
+                            scale_ring[slot * BN + i] = col < p.n ? __ldg(p.sb + int64_t(col) * kblocks + kb) : 0.f;
+                        }
+                        mbar_arrive(bar_ring_full + 8 * slot);
+                        if (++slot == kScaleRing) { slot = 0; phase ^= 1u; }
+                        if (kb == params_after) ok = stage_params(c);
                     }
-                    mbar_arrive(bar_ring_full + 8 * slot);
-                    if (++slot == kScaleRing) { slot = 0; phase ^= 1u; }
+                } else {
+                    ok = stage_params(c);
                 }
             }
         }
@@ -456,6 +493,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         uint32_t acc_phase = 0, ring_phase = 0;
         bool ok = true;
         const uint32_t my_stage = store_stage + (warp - 4) * S::kStoreBuffers * S::kStoreTile;
+        int tile_count = 0;  // tiles this CTA has finished: the phase of the parameter hand-over barriers
         float sa_ahead[2] = {0.f, 0.f};
         bool sa_ahead_valid = false;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
@@ -464,60 +502,55 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             const bool row_ok = row < p.m;
             const int col0 = c.n0 + half * kEpi;
             const float row_scale = S::kBlockScales ? 1.f : (row_ok ? __ldg(p.sa + row) : 0.f);
-            // The column parameters of this thread's part of the tile (weight scales, bias, residual scale) are only needed when the tile
-            // ends; asking for their cache lines now lets the tile epilogue find them in L1 instead of paying an L2 round trip per group.
-            if (p.vector_io && lane < 8) {
-                const char* line = nullptr;
-                if (lane < 4) line = S::kWGroup ? nullptr : reinterpret_cast<const char*>(p.sb + col0) + 128 * lane;
-                else if (lane < 6) line = bias ? reinterpret_cast<const char*>(bias + col0) + 128 * (lane - 4) : nullptr;
-                else line = rscale ? reinterpret_cast<const char*>(rscale + col0) + 128 * (lane - 6) : nullptr;
-                const int first_col = lane < 4 ? col0 + 32 * lane : lane < 6 ? col0 + 64 * (lane - 4) : col0 + 64 * (lane - 6);
-                if (line && first_col < p.n) asm volatile("prefetch.global.L1 [%0];" ::"l"(line));
-            }
+            // The tile's column parameters arrive in shared memory from warp 3; false when the CTA aborts.
+            auto await_params = [&]() -> bool {
+                if (!p.vector_io) return true;
+                return __all_sync(0xffffffffu, mbar_wait(bar_params_written, uint32_t(tile_count) & 1u, abort_flag, kTimeoutParams));
+            };
+            auto params_done = [&]() {
+                if (!p.vector_io) return;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_params_consumed);
+                ++tile_count;
+            };
 
-            // y values of 32 columns starting at `col`: bias, residual, one rounding, store
+            // y values of 32 columns starting at `col`: bias, residual, one rounding, store.  The accumulators of a tile live in registers,
+            // so this body is instantiated once per 32 columns of the thread: it is kept short (the tile epilogue runs once per tile and
+            // its instructions come from memory each time when the kernel outgrows the instruction cache).
             auto emit = [&](const float* v, int col) {
                 if (col >= p.n) return;
-                const bool staged = p.tma_y && col + 32 <= p.n;  // the same for the whole warp
-                if (!row_ok && !staged) return;
                 T* dst = y + int64_t(row) * p.n + col;
                 const T* res = residual && row_ok ? residual + int64_t(row) * p.n + col : nullptr;
-                uint32_t stage_row = 0;
-                if (staged) {
-                    // the TMA store that last read this buffer must be done with it before the warp writes it again
-                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(S::kStoreBuffers - 1) : "memory");
-                    __syncwarp();
-                    stage_row = my_stage + store_buffer * S::kStoreTile + lane * 64;
-                }
-                if (p.vector_io && col + 32 <= p.n) {
-                    // whole chunk, every operand 16-byte aligned: eight outputs per step with 128-bit accesses
+                if (p.vector_io) {
+                    // N is a multiple of 8 and every operand 16-byte aligned: eight outputs per step with 128-bit accesses; groups of eight
+                    // are whole or absent at the right edge, rows past M are clipped by the TMA store (or skipped by the plain one)
+                    const bool staged = p.tma_y != 0;
+                    const uint32_t stage_tile = my_stage + store_buffer * S::kStoreTile;
+                    if (staged) {
+                        // the TMA store that last read this buffer must be done with it before the warp writes it again
+                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(S::kStoreBuffers - 1) : "memory");
+                        __syncwarp();
+                    }
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
+                        if (col + j >= p.n) break;
                         float scale8[8], bias8[8], out[8];
-                        if constexpr (S::kWGroup || WQ_DIAG_VALUE == 4) {
+                        const int ct = col - c.n0 + j;  // column of the tile
+                        if constexpr (S::kWGroup) {
 #pragma unroll
                             for (int e = 0; e < 8; ++e) scale8[e] = 1.f;
                         } else {
-                            const float4 s0 = __ldg(reinterpret_cast<const float4*>(p.sb + col + j)), s1 = __ldg(reinterpret_cast<const float4*>(p.sb + col + j) + 1);
+                            const float4 s0 = *reinterpret_cast<const float4*>(param_sb + ct), s1 = *reinterpret_cast<const float4*>(param_sb + ct + 4);
                             scale8[0] = s0.x; scale8[1] = s0.y; scale8[2] = s0.z; scale8[3] = s0.w;
                             scale8[4] = s1.x; scale8[5] = s1.y; scale8[6] = s1.z; scale8[7] = s1.w;
                         }
-                        load_eight(bias + col + j, bias8, bias != nullptr);
+                        load_eight_plain(param_bias + ct, bias8);
 #pragma unroll
                         for (int e = 0; e < 8; ++e) out[e] = fmaf(v[j + e] * row_scale, scale8[e], bias8[e]);
                         if (res) {
                             float res8[8], rs8[8];
-                            const uint4 raw = *reinterpret_cast<const uint4*>(res + j);  // read before this thread overwrites it (y may be the residual)
-                            unpack_pair<T>(raw.x, res8[0], res8[1]);
-                            unpack_pair<T>(raw.y, res8[2], res8[3]);
-                            unpack_pair<T>(raw.z, res8[4], res8[5]);
-                            unpack_pair<T>(raw.w, res8[6], res8[7]);
-                            if (rscale) {
-                                load_eight(rscale + col + j, rs8, true);
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) rs8[e] = 1.f;
-                            }
+                            load_eight_plain(res + j, res8);  // read before this thread overwrites it (y may be the residual)
+                            load_eight_plain(param_rscale + ct, rs8);
 #pragma unroll
                             for (int e = 0; e < 8; ++e) out[e] = fmaf(out[e], rs8[e], res8[e]);
                         }
@@ -529,10 +562,10 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                         if (staged) {
                             // row `lane` of the staging tile, 16-byte piece j / 8 at its place in the 64-byte swizzle
                             const uint32_t piece = uint32_t(j >> 3) ^ ((uint32_t(lane) >> 1) & 3u);
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + piece * 16), "r"(packed.x), "r"(packed.y),
-                                         "r"(packed.z), "r"(packed.w)
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_tile + lane * 64 + piece * 16), "r"(packed.x),
+                                         "r"(packed.y), "r"(packed.z), "r"(packed.w)
                                          : "memory");
-                        } else {
+                        } else if (row_ok) {
                             *reinterpret_cast<uint4*>(dst + j) = packed;
                         }
                     }
@@ -541,7 +574,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                         __syncwarp();
                         if (lane == 0) {
                             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_y), "r"(col),
-                                         "r"(c.m0 + quarter * 32), "r"(my_stage + store_buffer * S::kStoreTile)
+                                         "r"(c.m0 + quarter * 32), "r"(stage_tile)
                                          : "memory");
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
@@ -549,15 +582,22 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     }
                     return;
                 }
-                // ragged or unaligned: one element at a time (fully unrolled: the accumulators must stay in registers)
+                // Odd N or unaligned operands: one element at a time.  The values go through this thread's 64 bytes of a staging tile
+                // (no TMA store is in flight in such a launch), 16 at a time, so that a short loop can index them.
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int cj = col + j;
-                    if (cj < p.n) {
-                        const float col_scale = S::kWGroup ? 1.f : __ldg(p.sb + cj);
-                        float value = fmaf(v[j] * row_scale, col_scale, bias ? as_float(bias[cj]) : 0.f);
-                        if (res) value = fmaf(value, rscale ? as_float(rscale[cj]) : 1.f, as_float(res[j]));
-                        dst[j] = round_one<T>(value);
+                for (int part = 0; part < 32; part += 16) {
+                    float* mine = store_stage_generic + ((warp - 4) * S::kStoreBuffers * S::kStoreTile + lane * 64) / 4;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) mine[j] = v[part + j];
+#pragma unroll 1
+                    for (int j = 0; j < 16; ++j) {
+                        const int cj = col + part + j;
+                        if (row_ok && cj < p.n) {
+                            const float col_scale = S::kWGroup ? 1.f : __ldg(p.sb + cj);
+                            float value = fmaf(mine[j] * row_scale, col_scale, bias ? as_float(bias[cj]) : 0.f);
+                            if (res) value = fmaf(value, rscale ? as_float(rscale[cj]) : 1.f, as_float(res[part + j]));
+                            dst[part + j] = round_one<T>(value);
+                        }
                     }
                 }
             };
@@ -643,13 +683,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                             for (int j = 0; j < 32; ++j) {
                                 float* a = &accf[chunk * 32 + j];
                                 if constexpr (MODE == kBlock) {
-#if defined(WQ_DIAG) && WQ_DIAG == 1
-                                    *a = v[j];  // diagnostic: conversion only
-#elif defined(WQ_DIAG) && WQ_DIAG == 2
-                                    *a = fmaf(__int_as_float(h[j]), sa_now, *a);  // diagnostic: one FMA on the raw bits, no conversion
-#else
                                     *a = fmaf(v[j], sa_now, *a);
-#endif
                                 } else if constexpr (MODE == kBlockG) {
                                     *a = fmaf(v[j], sa_now * ring[chunk * 32 + j], *a);
                                 } else {
@@ -701,15 +735,10 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                 if (warp == 4 && lane == 0) WQ_STAMP(4096, (t / int(gridDim.x)) * kblocks + kblocks - 1, 6);
 #endif
                 if constexpr (!DUMP) {
-#if WQ_DIAG_VALUE == 5
-                    float total = 0.f;  // diagnostic: no tile epilogue at all
-#pragma unroll
-                    for (int j = 0; j < kEpi; ++j) total += accf[j];
-                    if (total == 123.456f) y[row] = round_one<T>(total);
-#else
+                    if (!(ok = await_params())) break;
 #pragma unroll
                     for (int chunk = 0; chunk < kEpi / 32; ++chunk) emit(&accf[chunk * 32], col0 + chunk * 32);
-#endif
+                    params_done();
                 }
 #ifdef WQ_TRACE
                 if (warp == 4 && lane == 0) WQ_STAMP(4096, (t / int(gridDim.x)) * kblocks + kblocks - 1, 7);
@@ -718,6 +747,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                 if (!(ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, kTimeoutTmemFull)))) break;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + lane_base + acc * S::kAccColumns + half * kEpi;
+                if (!(ok = await_params())) break;
 #pragma unroll 1
                 for (int chunk = 0; chunk < kEpi / 32; ++chunk) {
                     int s_hi[32], s_lo[32];
@@ -738,6 +768,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     }
                     emit(v, col0 + chunk * 32);
                 }
+                params_done();
                 if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1u; }
             }
         }
