@@ -61,9 +61,10 @@ int wq8_rotate_groups(const void* x, void* out, int m, int k, int64_t ldx, int d
  *   10, 11   'block'    sa (M, ceil(K/128))  sb (N)
  *   12, 13   'block+g'  sa (M, ceil(K/128))  sb (N, ceil(K/128))
  *   14       'exact+g'  sa (M), a_lo given   sb (N, ceil(K/128))
- * a_lo must be non-NULL exactly for variants 1, 7, 14 (else -2).  split: 0 = whole tiles, 1 = tiles may be
- * split along K when they leave SMs idle.  workspace / counters: sizes from wq8_gemm_workspace(); counters
- * must be zero on entry and are left zero.  sms: SM count of the device.  Replaces int8_gemm.cu:1648-1656. */
+ * a_lo must be non-NULL exactly for variants 1, 7, 14 (else -2).  split: accepted, tiles are never split along K
+ * here.  workspace / counters: sizes from wq8_gemm_workspace(); variants 12-14 regroup the weight scales by
+ * block of K into the workspace (16-byte aligned; NULL is -2), the other variants use neither.  sms: SM count
+ * of the device.  Replaces int8_gemm.cu:1648-1656. */
 int wq8_gemm(const int8_t* a, const int8_t* a_lo, const float* sa, const int8_t* b, const float* sb, const void* bias,
              const void* residual, const void* rscale, void* y, int m, int n, int k, int dtype, int variant, int sms, int split,
              int* workspace, int* counters, wq8_stream_t stream);

@@ -34,8 +34,8 @@ constexpr int kEpilogueWarps = 8;
 constexpr int kRearmWarps = 4;       // one per lane quarter of tensor memory: they put the conversion bias back into drained accumulators
 constexpr int kThreads = 32 * (4 + kEpilogueWarps + kRearmWarps);
 // Registers per thread after the split (setmaxnreg): 512 threads are launched with 128 each; the control and re-arm warps keep 40 and
-// the epilogue warps, which hold a tile's FP32 accumulators, take 208: 256 x 40 + 256 x 208 = 63488 of the 65536.
-constexpr int kSmallRegs = 40, kEpilogueRegs = 208;
+// the epilogue warps, which hold a tile's FP32 accumulators, take 216: 256 x 40 + 256 x 216 = all 65536.
+constexpr int kSmallRegs = 40, kEpilogueRegs = 216;
 constexpr int kScaleRing = 4;        // blocks of gathered weight scales in flight
 constexpr long long kWaitLimit = 4000000000ll;  // clocks (about two seconds) before a wait gives up
 
@@ -226,6 +226,8 @@ struct GemmParams {
     int m, n, k;
     int tiles_m, tiles_n;
     int vector_io;  // y, residual, sb, bias and rscale allow 16-byte accesses (N multiple of 8, aligned bases)
+    const float* sb_blocks;  // group-scaled weights: the scales regrouped by block, (ceil(K/128), n_pad) with zeros past N
+    int n_pad;               // row length of sb_blocks: N rounded up to 256
     int tma_y;      // map_y describes y: whole 32-column chunks leave through shared memory and the TMA unit
 };
 
@@ -288,7 +290,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         mbar_init(bar_params_written, 32);
         mbar_init(bar_params_consumed, kEpilogueWarps);
         for (int s = 0; s < kScaleRing; ++s) {
-            mbar_init(bar_ring_full + 8 * s, 32);
+            mbar_init(bar_ring_full + 8 * s, 1);
             mbar_init(bar_ring_empty + 8 * s, kEpilogueWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -446,11 +448,15 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     const int params_after = (kblocks < 2 ? kblocks : 2) - 1;
                     for (int kb = 0; kb < kblocks && ok; ++kb) {
                         if (!(ok = mbar_wait(bar_ring_empty + 8 * slot, phase ^ 1u, abort_flag, kTimeoutScales))) break;
-                        for (int i = lane; i < BN; i += 32) {
-                            const int col = c.n0 + i;
-                            scale_ring[slot * BN + i] = col < p.n ? __ldg(p.sb + int64_t(col) * kblocks + kb) : 0.f;
+                        // the tile's BN scales of this block are contiguous in sb_blocks: one bulk copy, up to kScaleRing of them in flight
+                        if (lane == 0) {
+                            mbar_expect_tx(bar_ring_full + 8 * slot, BN * 4);
+                            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                             smem_u32(scale_ring + slot * BN)),
+                                         "l"(p.sb_blocks + int64_t(kb) * p.n_pad + c.n0), "r"(BN * 4), "r"(bar_ring_full + 8 * slot)
+                                         : "memory");
                         }
-                        mbar_arrive(bar_ring_full + 8 * slot);
+                        __syncwarp();
                         if (++slot == kScaleRing) { slot = 0; phase ^= 1u; }
                         if (kb == params_after) ok = stage_params(c);
                     }
@@ -890,7 +896,21 @@ static bool make_output_map(CUtensorMap* map, const void* base, int m, int n, bo
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Weight scales of group-scaled weights, (N, kblocks) as the caller holds them -> (kblocks, n_pad) with zeros past N, so that the scales
+// a tile needs for one block of K are one contiguous run.
+__global__ void regroup_weight_scales(const float* __restrict__ sb, float* __restrict__ out, int n, int kblocks, int n_pad) {
+    const int64_t total = int64_t(kblocks) * n_pad;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+        const int kb = int(i / n_pad), col = int(i % n_pad);
+        out[i] = col < n ? __ldg(sb + int64_t(col) * kblocks + kb) : 0.f;
+    }
+}
+
+constexpr int kScalePad = 256;
+static int padded_n(int n) { return (n + kScalePad - 1) / kScalePad * kScalePad; }
+
 struct GemmArgs {
+    float* scale_scratch;  // group-scaled weights: (ceil(K/128), padded_n(N)) floats of caller workspace
     const int8_t* a;
     const int8_t* a_lo;
     const float* sa;
@@ -932,6 +952,14 @@ static int launch(const GemmArgs& g, cudaStream_t stream) {
     p.tiles_n = (g.n + BN - 1) / BN;
     const uintptr_t bases = reinterpret_cast<uintptr_t>(g.y) | reinterpret_cast<uintptr_t>(g.residual) | reinterpret_cast<uintptr_t>(g.bias) |
                             reinterpret_cast<uintptr_t>(g.rscale) | (S::kWGroup ? 0 : reinterpret_cast<uintptr_t>(g.sb));
+    if (S::kWGroup) {
+        if (!g.scale_scratch || (reinterpret_cast<uintptr_t>(g.scale_scratch) & 15)) return -2;
+        const int kblocks = (g.k + kStageK - 1) / kStageK;
+        p.n_pad = padded_n(g.n);
+        p.sb_blocks = g.scale_scratch;
+        const int64_t total = int64_t(kblocks) * p.n_pad;
+        regroup_weight_scales<<<int((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184), 256, 0, stream>>>(g.sb, g.scale_scratch, g.n, kblocks, p.n_pad);
+    }
     p.vector_io = g.n % 8 == 0 && (bases & 15) == 0;
     p.tma_y = !DUMP && p.vector_io && make_output_map(&map_y, g.y, g.m, g.n, std::is_same<T, bf16>::value);
     if (!p.tma_y) map_y = map_a;
@@ -960,19 +988,23 @@ template <class T> static int dispatch(const GemmArgs& g, int variant, cudaStrea
 using namespace wq;
 
 WQ_API int wq8_gemm(const int8_t* a, const int8_t* a_lo, const float* sa, const int8_t* b, const float* sb, const void* bias, const void* residual,
-                    const void* rscale, void* y, int m, int n, int k, int dtype, int variant, int sms, int /*split*/, int* /*workspace*/,
+                    const void* rscale, void* y, int m, int n, int k, int dtype, int variant, int sms, int /*split*/, int* workspace,
                     int* /*counters*/, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if ((variant == 1 || variant == 7 || variant == 14) != (a_lo != nullptr)) return -2;
     if (k <= 0 || k % 16) return -2;
-    const GemmArgs g{a, a_lo, sa, b, sb, bias, residual, rscale, y, nullptr, m, n, k, sms};
+    const GemmArgs g{reinterpret_cast<float*>(workspace), a, a_lo, sa, b, sb, bias, residual, rscale, y, nullptr, m, n, k, sms};
     if (dtype == 0) return dispatch<__half>(g, variant, stream);
     if (dtype == 1) return dispatch<bf16>(g, variant, stream);
     return -1;
 }
 
-// Whole tiles only: no partial-sum workspace, no counters.
-WQ_API void wq8_gemm_workspace(int, int, int, int, int, int, int64_t* sizes) { sizes[0] = sizes[1] = 0; }
+// Whole tiles only: no partial sums, no counters.  The variants with group-scaled weights regroup the weight scales by block of K
+// into the workspace.
+WQ_API void wq8_gemm_workspace(int, int n, int k, int variant, int, int, int64_t* sizes) {
+    sizes[0] = sizes[1] = 0;
+    if (variant >= 12 && variant <= 14 && n > 0 && k > 0) sizes[0] = int64_t((k + kStageK - 1) / kStageK) * padded_n(n) * 4;
+}
 
 WQ_API int wq8_gemm_select(int, int, int, int hilo, int) { return hilo ? 1 : 0; }
 
@@ -984,7 +1016,7 @@ WQ_API int wq8_gemm_segments(const int8_t*, const int8_t*, const float*, const i
 WQ_API int wq8_debug_block_sums(const int8_t* a, const int8_t* b, int32_t* sums, int m, int n, int k, int sms, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (k <= 0 || k % 16) return -2;
-    const GemmArgs g{a, nullptr, nullptr, b, nullptr, nullptr, nullptr, nullptr, nullptr, sums, m, n, k, sms};
+    const GemmArgs g{nullptr, a, nullptr, nullptr, b, nullptr, nullptr, nullptr, nullptr, nullptr, sums, m, n, k, sms};
     return launch<bf16, kBlock, 256, kFoldAdd, true>(g, stream);
 }
 
