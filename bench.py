@@ -181,6 +181,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--workload", default="c1", choices=sorted(DESCRIPTIONS) + sorted(FEW_TOKEN))
     parser.add_argument("--tokens", type=int, default=1, help="token count of the few-token workloads (c3u, c3d)")
+    parser.add_argument("--rows", type=int, default=None, help="rows of the block workloads (default: the configuration's own; a smaller "
+                        "case of the same shape is what a profiler capture wants)")
     parser.add_argument("--path", default=None, help="path of the few-token workloads: lines, small or exact (default: by token count)")
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-cpu-baseline", action="store_true")
@@ -208,7 +210,7 @@ def main():
     name = args.workload
     _, k, n_total = workloads.SHAPES[name]
     start, stop = wdist.shard_bounds(n_total, world, rank)
-    c = workloads.make(name, n_offset=start, n_rows=stop - start)
+    c = workloads.make(name, rows=args.rows, n_offset=start, n_rows=stop - start)
     m = c.m
     ops = 2 * m * n_total * k
     host_x = c.x.pin_memory()
@@ -304,6 +306,7 @@ def main():
         peak, peak_source = 2 * peaks["bf16_tflops_sustained"], "2 x MEASURED_PEAKS bf16_tflops_sustained (INT8 MMA rate = 2 x BF16), of measured"
     else:
         peak, peak_source = 2 * 1400.0, "2 x 1.4 PFLOP/s sustained bf16, of fallback"
+    launches_per_step = 2 + (1 if g.scale.dim() == 2 else 0)  # quantizer, GEMM, and the regrouping of group-scaled weight scales
     quant_bytes = m * k * (2 if c.act != "swiglu" else 4) + m * k + 4 * m * ((k + 127) // 128)
     line = {
         "metric": METRIC, "value": ops * args.steps / (total_ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
@@ -312,13 +315,19 @@ def main():
         "config": {"workload": f"{name}: {DESCRIPTIONS[name]}", "global_rows": m, "n": n_total, "k": k,
                    "parallelism": "single GPU" if world == 1 else f"output channels sharded x{world}, replicated activation, NCCL all_gather of the output",
                    "l2": "no flush: the operands of a step (x, q, W, y: > 1 GB) exceed the 126 MB L2"},
-        "e2e": e2e, "gpu_launches": 2 * args.steps, "clocks": clocks,
+        "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
         "roofline": {"kernel": "gemm_i8_tc (block mode)", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                      "peak_source": peak_source, "nominal_dense_int8_tops": 4500.0, "traffic": None, "kernel_ms": gemm_ms,
                      "quantizer": {"kernel_ms": quant_ms, "bound": "hbm", "achieved": quant_bytes / (quant_ms * 1e-3) / 1e9, "unit": "GB/s",
                                    "peak": peaks["hbm_gbs"] if peaks else 6650.0, "algorithmic_bytes": quant_bytes}},
         "device_status": status,
     }
+    if world == 1:
+        # this library's own probe of the INT8 tensor pipe (MMAs alone on resident pseudo-random operands), measured now on this GPU: the
+        # ceiling of any kind::i8 kernel at the clocks this board holds under that load
+        probe_tops, probe_mhz, _ = wq.debug_mma_peak("i8", 4000, True)
+        line["roofline"]["tensor_probe"] = {"int8_tops": probe_tops, "sm_mhz": probe_mhz, "frac": achieved / probe_tops,
+                                            "what": "tcgen05 kind::i8 M128 N256 issue rate, all SMs, pseudo-random operands"}
     if not args.no_cpu_baseline and world == 1:
         rows = 512
         tops, seconds, _ = cpu_reference_tops(name, rows, 3)

@@ -617,3 +617,15 @@ def debug_block_sums(a, b):
 def debug_status():
     """Status word of the GEMM pipeline (0 = no bounded wait gave up); synchronizes the device."""
     return _require().wq8_debug_status()
+
+
+def debug_mma_peak(kind="i8", groups=4000, random_operands=True, device=None):
+    """Issue-rate probe of the tensor pipe on the current device: (TOPS of the whole GPU, SM MHz during the probe, clocks per group of
+    four M128 N256 MMAs).  kind "i8" (tcgen05 kind::i8) or "bf16" (kind::f16).  A measurement tool: allocates and synchronizes."""
+    lib = _require()
+    lib.wq8_debug_mma_peak.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+    lib.wq8_debug_mma_peak.restype = ctypes.c_int
+    results = (ctypes.c_double * 3)()
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    _check(lib.wq8_debug_mma_peak(0 if kind == "i8" else 1, -groups if random_operands else groups, _sm_count(device), results))
+    return results[0], results[1], results[2]
