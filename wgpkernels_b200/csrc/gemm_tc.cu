@@ -86,14 +86,11 @@ WQ_DEVICE bool mbar_test(uint32_t bar, uint32_t parity) {
 }
 
 // Waits for the phase of `parity`; false when the CTA is aborting or the wait ran out (then `code` is recorded and the abort flag raised).
-// RELAXED: for a role that runs well ahead of its consumer (the TMA producer, the column-parameter warp): it sleeps between looks, so
-// that its polling does not take issue slots from the epilogue warps of its scheduler.
-template <bool RELAXED = false> WQ_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+WQ_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
     if (mbar_test(bar, parity)) return true;
     const long long start = clock64();
     for (uint32_t spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (RELAXED) __nanosleep(128);
         if ((spin & 15u) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - start > kWaitLimit) {
@@ -332,7 +329,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
                 const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n);
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!(ok = mbar_wait<true>(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kTimeoutEmpty))) break;
+                    if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kTimeoutEmpty))) break;
                     const uint32_t full = bar_full + 8 * stage;
                     const uint32_t dst = smem_u32(smem + stage * S::kStageBytes);
                     mbar_expect_tx(full, S::kStageBytes);
@@ -432,7 +429,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             auto stage_params = [&](const TileCoord& c) -> bool {
                 if (!p.vector_io) return true;
                 // every epilogue warp is done with the previous tile's parameters
-                if (tile_count > 0 && !mbar_wait<true>(bar_params_consumed, uint32_t(tile_count - 1) & 1u, abort_flag, kTimeoutParams)) return false;
+                if (tile_count > 0 && !mbar_wait(bar_params_consumed, uint32_t(tile_count - 1) & 1u, abort_flag, kTimeoutParams)) return false;
                 for (int i = lane; i < BN; i += 32) {
                     const int col = c.n0 + i;
                     const bool inside = col < p.n;
@@ -450,7 +447,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     // the first two blocks' scales go first: the epilogue warps start on them right after the previous tile's write-out
                     const int params_after = (kblocks < 2 ? kblocks : 2) - 1;
                     for (int kb = 0; kb < kblocks && ok; ++kb) {
-                        if (!(ok = mbar_wait<true>(bar_ring_empty + 8 * slot, phase ^ 1u, abort_flag, kTimeoutScales))) break;
+                        if (!(ok = mbar_wait(bar_ring_empty + 8 * slot, phase ^ 1u, abort_flag, kTimeoutScales))) break;
                         // the tile's BN scales of this block are contiguous in sb_blocks: one bulk copy, up to kScaleRing of them in flight
                         if (lane == 0) {
                             mbar_expect_tx(bar_ring_full + 8 * slot, BN * 4);
