@@ -181,6 +181,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--workload", default="c1", choices=sorted(DESCRIPTIONS) + sorted(FEW_TOKEN))
     parser.add_argument("--tokens", type=int, default=1, help="token count of the few-token workloads (c3u, c3d)")
+    parser.add_argument("--gather", choices=["fused", "nccl"], default="fused", help="N > 1: how the output slices reach every rank: written "
+                        "by the GEMM's tile epilogue into all ranks' buffers (fused), or an NCCL all-gather after the GEMM")
     parser.add_argument("--rows", type=int, default=None, help="rows of the block workloads (default: the configuration's own; a smaller "
                         "case of the same shape is what a profiler capture wants)")
     parser.add_argument("--path", default=None, help="path of the few-token workloads: lines, small or exact (default: by token count)")
@@ -225,6 +227,9 @@ def main():
         if layer is None:
             return wq.linear(x, g.weight, g.scale, g.bias, mode="block", act=c.act, act_weight=g.act_weight, eps=c.eps, residual=g.residual,
                              residual_scale=g.residual_scale, out=g.residual if in_place else None)
+        if args.gather == "fused":  # every rank's GEMM writes its columns into all ranks' (M, N) buffers: no collective on the data
+            return layer(x, gather="fused", mode="block", act=c.act, act_weight=g.act_weight, eps=c.eps, residual=g.residual,
+                         residual_scale=g.residual_scale)
         return layer(x, gather="full", mode="block", act=c.act, act_weight=g.act_weight, eps=c.eps, residual=g.residual,
                      residual_scale=g.residual_scale, out=g.residual if in_place else None)
 
@@ -313,7 +318,9 @@ def main():
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "tokens_per_s": m * args.steps / (total_ms * 1e-3),
         "config": {"workload": f"{name}: {DESCRIPTIONS[name]}", "global_rows": m, "n": n_total, "k": k,
-                   "parallelism": "single GPU" if world == 1 else f"output channels sharded x{world}, replicated activation, NCCL all_gather of the output",
+                   "parallelism": "single GPU" if world == 1 else (f"output channels sharded x{world}, replicated activation, output written into every rank's buffer by the GEMM epilogue (TMA "
+                                   "stores over NVLink)" if args.gather == "fused" else
+                                   f"output channels sharded x{world}, replicated activation, NCCL all_gather of the output"),
                    "l2": "no flush: the operands of a step (x, q, W, y: > 1 GB) exceed the 126 MB L2"},
         "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
         "roofline": {"kernel": "gemm_i8_tc (block mode)", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,

@@ -106,6 +106,16 @@ void wq8_l2_flush_release(void);
  * tests use to check the INT32 sums bit for bit. */
 int wq8_debug_block_sums(const int8_t* a, const int8_t* b, int32_t* sums, int m, int n, int k, int sms, wq8_stream_t stream);
 
+/* wq8_gemm with `count` (1 to 8) destinations of the same output: ys is a HOST array of device pointers, each to the first element
+ * of an (M, N) block with row stride ld_y (elements) inside a wider matrix; the residual has row stride ld_residual.  The rank of an
+ * N-sharded layer passes the position of its output columns in the full-width (M, N_total) buffers of all ranks (its own first;
+ * the others peer-mapped), and the all-gather of the output happens inside the GEMM: the tile epilogue issues one TMA store per
+ * destination.  Needs N, ld_y, ld_residual multiples of 8 and 16-byte aligned pointers when count > 1 (-2 otherwise).  The caller
+ * orders the launch against the readers of the destinations (a barrier over the ranks before and after).  No split, no counters. */
+int wq8_gemm_multi(const int8_t* a, const int8_t* a_lo, const float* sa, const int8_t* b, const float* sb, const void* bias,
+                   const void* residual, int64_t ld_residual, const void* rscale, void* const* ys, int count, int64_t ld_y, int m, int n, int k,
+                   int dtype, int variant, int sms, int* workspace, wq8_stream_t stream);
+
 /* wq8_small for callers that cannot allocate device memory (no counterpart in the reference, which always takes caller scratch).
  * A host that reaches this library through a bare FFI with buffers it was handed, a serving loop under a fixed memory budget, code
  * running during CUDA graph capture or in a section where cudaMalloc is not allowed: none of them can supply the K-split scratch

@@ -156,3 +156,34 @@ def test_full_size_partition_invariance(wq):
     assert torch.isfinite(checksum).all()
     again = wq.linear_prepared(prepared, c.weight, c.scale, c.bias)
     assert torch.equal(full, again)
+
+
+@pytest.mark.parametrize("mode", ["row", "exact", "block", "block+g", "exact+g"])
+@pytest.mark.parametrize("residual", [False, True], ids=["plain", "residual"])
+def test_column_ranges_and_several_outputs(wq, mode, residual):
+    """out / residual as column ranges of wider matrices, and a list of outputs (what an N-sharded rank passes: its columns inside the
+    full-width buffers of all ranks): every destination equals the contiguous result bit for bit, nothing else is touched."""
+    m, n, k, dtype = 300, 520, 640, torch.bfloat16
+    base, a, a_lo, sa, b, sb, bias, res, rs = operands(mode, m, n, k, dtype, 77, residual)
+    dev = lambda t: None if t is None else t.cuda()
+    expected = wq.gemm(dev(a), dev(a_lo), dev(sa), dev(b), dev(sb), dev(bias), dtype, 0, MODES[mode], residual=dev(res), residual_scale=dev(rs))
+    wide = [torch.full((m, 1024), 7.0, dtype=dtype, device="cuda") for _ in range(3)]  # the destinations share one row stride
+    offsets = [64, 256, 8]
+    views = [w[:, o:o + n] for w, o in zip(wide, offsets)]
+    wide_residual = None
+    if residual:
+        wide_residual = torch.zeros((m, 2048), dtype=dtype, device="cuda")
+        wide_residual[:, 1024:1024 + n] = res.cuda()
+    got = wq.gemm(dev(a), dev(a_lo), dev(sa), dev(b), dev(sb), dev(bias), dtype, 0, MODES[mode], out=views,
+                  residual=None if wide_residual is None else wide_residual[:, 1024:1024 + n], residual_scale=dev(rs))
+    torch.cuda.synchronize()
+    assert got.data_ptr() == views[0].data_ptr()
+    for w, o in zip(wide, offsets):
+        assert torch.equal(w[:, o:o + n], expected)
+        assert bool((w[:, :o] == 7.0).all()) and bool((w[:, o + n:] == 7.0).all())
+    # one strided output, odd width (element-wise epilogue)
+    odd = torch.full((m, 1000), 7.0, dtype=dtype, device="cuda")
+    expected_odd = wq.gemm(dev(a), dev(a_lo), dev(sa), dev(b[:515]), dev(sb[:515]), dev(bias[:515]), dtype, 0, MODES[mode])
+    wq.gemm(dev(a), dev(a_lo), dev(sa), dev(b[:515]), dev(sb[:515]), dev(bias[:515]), dtype, 0, MODES[mode], out=odd[:, 3:518])
+    assert torch.equal(odd[:, 3:518], expected_odd) and bool((odd[:, :3] == 7.0).all()) and bool((odd[:, 518:] == 7.0).all())
+    assert wq.debug_status() == 0

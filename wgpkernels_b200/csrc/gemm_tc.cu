@@ -228,8 +228,15 @@ struct GemmParams {
     int vector_io;  // y, residual, sb, bias and rscale allow 16-byte accesses (N multiple of 8, aligned bases)
     const float* sb_blocks;  // group-scaled weights: the scales regrouped by block, (ceil(K/128), n_pad) with zeros past N
     int n_pad;               // row length of sb_blocks: N rounded up to 256
-    int tma_y;      // map_y describes y: whole 32-column chunks leave through shared memory and the TMA unit
+    int tma_y;      // the output maps describe the destinations: whole 32-column chunks leave through shared memory and the TMA unit
+    int destinations;  // copies of the output written by the TMA stores (1, or one per GPU of an N-sharded layer)
+    int64_t ld_y, ld_residual;  // row strides in elements of y and of the residual
 };
+
+// Up to eight destinations of the output: the same (M, N) block in this GPU's buffer and, for an N-sharded layer, in the buffers of its
+// peers (ordinary TMA stores over NVLink; nothing is ever loaded from a peer).
+constexpr int kMaxDestinations = 8;
+struct OutputMaps { CUtensorMap map[kMaxDestinations]; };
 
 struct TileCoord { int m0, n0; };
 // Bands of 16 row tiles are swept over all column tiles, so the CTAs running together share a few A bands and B tiles in L2.
@@ -243,7 +250,7 @@ template <int BN> WQ_DEVICE TileCoord tile_origin(int t, int tiles_m, int tiles_
 template <class T, int MODE, int BN, int FOLD, bool DUMP>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b,
-           const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
+           const __grid_constant__ OutputMaps out_maps, const GemmParams p) {
     using S = Shape<MODE, BN>;
     constexpr int kStages = S::kStages, kAccBuffers = S::kAccBuffers, kEpi = S::kEpiColumns;
     // No static shared memory in this kernel: the dynamic block starts at the CTA's shared window, which is 1024-byte aligned (the
@@ -297,7 +304,8 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
         if (S::kHilo) prefetch_tensormap(&map_a_lo);
-        if (p.tma_y) prefetch_tensormap(&map_y);
+        if (p.tma_y)
+            for (int d = 0; d < p.destinations; ++d) prefetch_tensormap(&out_maps.map[d]);
     }
     if (warp == 2) tmem_alloc(smem_u32(&tmem_slot), kTmemColumns);
     tc_fence_before();
@@ -525,8 +533,8 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             // its instructions come from memory each time when the kernel outgrows the instruction cache).
             auto emit = [&](const float* v, int col) {
                 if (col >= p.n) return;
-                T* dst = y + int64_t(row) * p.n + col;
-                const T* res = residual && row_ok ? residual + int64_t(row) * p.n + col : nullptr;
+                T* dst = y + int64_t(row) * p.ld_y + col;
+                const T* res = residual && row_ok ? residual + int64_t(row) * p.ld_residual + col : nullptr;
                 if (p.vector_io) {
                     // N is a multiple of 8 and every operand 16-byte aligned: eight outputs per step with 128-bit accesses; groups of eight
                     // are whole or absent at the right edge, rows past M are clipped by the TMA store (or skipped by the plain one)
@@ -579,9 +587,10 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         __syncwarp();
                         if (lane == 0) {
-                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_y), "r"(col),
-                                         "r"(c.m0 + quarter * 32), "r"(stage_tile)
-                                         : "memory");
+                            for (int d = 0; d < p.destinations; ++d)
+                                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&out_maps.map[d]),
+                                             "r"(col), "r"(c.m0 + quarter * 32), "r"(stage_tile)
+                                             : "memory");
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
                         if (++store_buffer == S::kStoreBuffers) store_buffer = 0;
@@ -884,11 +893,11 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int k, int bo
 }
 
 // (m, n) row-major matrix of 16-bit outputs -> tensor map with boxes of 32 rows x 32 columns, 64-byte swizzle (stores clip at the edges).
-static bool make_output_map(CUtensorMap* map, const void* base, int m, int n, bool is_bf16) {
+static bool make_output_map(CUtensorMap* map, const void* base, int m, int n, int64_t ld, bool is_bf16) {
     EncodeTiled encode = encode_tiled();
     if (!encode) return false;
     const cuuint64_t dims[2] = {cuuint64_t(n), cuuint64_t(m)};
-    const cuuint64_t strides[1] = {cuuint64_t(n) * 2};
+    const cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
     const cuuint32_t box[2] = {32, 32};
     const cuuint32_t elem[2] = {1, 1};
     return encode(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box,
@@ -922,6 +931,9 @@ struct GemmArgs {
     void* y;
     int* dump;
     int m, n, k, sms;
+    void* const* ys = nullptr;  // `count` destinations of the output (host array of device pointers); y when null
+    int count = 1;
+    int64_t ld_y = 0, ld_residual = 0;  // 0: contiguous (N)
 };
 
 template <class T, int MODE, int BN, int FOLD, bool DUMP>
@@ -938,7 +950,8 @@ static int launch(const GemmArgs& g, cudaStream_t stream) {
     }
     if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15) || (g.a_lo && (reinterpret_cast<uintptr_t>(g.a_lo) & 15)))
         return -2;
-    CUtensorMap map_a, map_a_lo, map_b, map_y;
+    CUtensorMap map_a, map_a_lo, map_b;
+    OutputMaps out_maps;
     if (!make_map(&map_a, g.a, g.m, g.k, kBM) || !make_map(&map_b, g.b, g.n, g.k, BN)) return int(cudaErrorNotSupported);
     if (S::kHilo) {
         if (!make_map(&map_a_lo, g.a_lo, g.m, g.k, kBM)) return int(cudaErrorNotSupported);
@@ -946,11 +959,16 @@ static int launch(const GemmArgs& g, cudaStream_t stream) {
         map_a_lo = map_a;
     }
     GemmParams p{};
-    p.sa = g.sa; p.sb = g.sb; p.bias = g.bias; p.residual = g.residual; p.rscale = g.rscale; p.y = g.y; p.dump = g.dump;
+    p.sa = g.sa; p.sb = g.sb; p.bias = g.bias; p.residual = g.residual; p.rscale = g.rscale; p.dump = g.dump;
+    p.y = g.ys ? g.ys[0] : g.y;
+    p.ld_y = g.ld_y ? g.ld_y : g.n;
+    p.ld_residual = g.ld_residual ? g.ld_residual : g.n;
+    p.destinations = g.ys ? g.count : 1;
+    if (p.destinations < 1 || p.destinations > kMaxDestinations) return -2;
     p.m = g.m; p.n = g.n; p.k = g.k;
     p.tiles_m = (g.m + kBM - 1) / kBM;
     p.tiles_n = (g.n + BN - 1) / BN;
-    const uintptr_t bases = reinterpret_cast<uintptr_t>(g.y) | reinterpret_cast<uintptr_t>(g.residual) | reinterpret_cast<uintptr_t>(g.bias) |
+    uintptr_t bases = reinterpret_cast<uintptr_t>(p.y) | reinterpret_cast<uintptr_t>(g.residual) | reinterpret_cast<uintptr_t>(g.bias) |
                             reinterpret_cast<uintptr_t>(g.rscale) | (S::kWGroup ? 0 : reinterpret_cast<uintptr_t>(g.sb));
     if (S::kWGroup) {
         if (!g.scale_scratch || (reinterpret_cast<uintptr_t>(g.scale_scratch) & 15)) return -2;
@@ -960,13 +978,20 @@ static int launch(const GemmArgs& g, cudaStream_t stream) {
         const int64_t total = int64_t(kblocks) * p.n_pad;
         regroup_weight_scales<<<int((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184), 256, 0, stream>>>(g.sb, g.scale_scratch, g.n, kblocks, p.n_pad);
     }
-    p.vector_io = g.n % 8 == 0 && (bases & 15) == 0;
-    p.tma_y = !DUMP && p.vector_io && make_output_map(&map_y, g.y, g.m, g.n, std::is_same<T, bf16>::value);
-    if (!p.tma_y) map_y = map_a;
+    for (int d = 1; d < p.destinations; ++d) bases |= reinterpret_cast<uintptr_t>(g.ys[d]);
+    p.vector_io = g.n % 8 == 0 && p.ld_y % 8 == 0 && p.ld_residual % 8 == 0 && (bases & 15) == 0;
+    p.tma_y = !DUMP && p.vector_io;
+    for (int d = 0; d < kMaxDestinations; ++d) {
+        if (p.tma_y && d < p.destinations)
+            p.tma_y = make_output_map(&out_maps.map[d], d == 0 ? p.y : g.ys[d], g.m, g.n, p.ld_y, std::is_same<T, bf16>::value);
+        else
+            out_maps.map[d] = map_a;
+    }
+    if (p.destinations > 1 && !p.tma_y) return -2;  // several destinations are only written by the TMA stores
     const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
     const int sms = g.sms > 0 ? g.sms : 148;
     const int grid = int(tiles < sms ? tiles : sms);
-    kernel<<<grid, kThreads, S::kSmemBytes, stream>>>(map_a, map_a_lo, map_b, map_y, p);
+    kernel<<<grid, kThreads, S::kSmemBytes, stream>>>(map_a, map_a_lo, map_b, out_maps, p);
     return int(cudaGetLastError());
 }
 
@@ -994,6 +1019,28 @@ WQ_API int wq8_gemm(const int8_t* a, const int8_t* a_lo, const float* sa, const 
     if ((variant == 1 || variant == 7 || variant == 14) != (a_lo != nullptr)) return -2;
     if (k <= 0 || k % 16) return -2;
     const GemmArgs g{reinterpret_cast<float*>(workspace), a, a_lo, sa, b, sb, bias, residual, rscale, y, nullptr, m, n, k, sms};
+    if (dtype == 0) return dispatch<__half>(g, variant, stream);
+    if (dtype == 1) return dispatch<bf16>(g, variant, stream);
+    return -1;
+}
+
+// wq8_gemm whose output goes to `count` destinations at once (ys: host array of device pointers to the first element of an (M, N)
+// block with row stride ld_y; the residual has row stride ld_residual): the rank of an N-sharded layer writes its output columns
+// straight into the full-width buffers of all ranks.  Destinations in a peer GPU's memory are written by TMA stores over NVLink.
+WQ_API int wq8_gemm_multi(const int8_t* a, const int8_t* a_lo, const float* sa, const int8_t* b, const float* sb, const void* bias,
+                          const void* residual, int64_t ld_residual, const void* rscale, void* const* ys, int count, int64_t ld_y, int m, int n,
+                          int k, int dtype, int variant, int sms, int* workspace, cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (!ys || count < 1 || count > kMaxDestinations || ld_y < n || (residual && ld_residual < n)) return -2;
+    for (int d = 0; d < count; ++d)
+        if (!ys[d]) return -2;
+    if ((variant == 1 || variant == 7 || variant == 14) != (a_lo != nullptr)) return -2;
+    if (k <= 0 || k % 16) return -2;
+    GemmArgs g{reinterpret_cast<float*>(workspace), a, a_lo, sa, b, sb, bias, residual, rscale, ys[0], nullptr, m, n, k, sms};
+    g.ys = ys;
+    g.count = count;
+    g.ld_y = ld_y;
+    g.ld_residual = residual ? ld_residual : 0;
     if (dtype == 0) return dispatch<__half>(g, variant, stream);
     if (dtype == 1) return dispatch<bf16>(g, variant, stream);
     return -1;

@@ -6,6 +6,11 @@ and bias (loaded once; the weight never moves).  The activation is present on ev
 rank 0 here); every rank quantizes it itself -- recomputing the quantization costs less than moving the INT8 copy over NVLink -- and
 runs the GEMM on its own output channels.  The one collective is the all-gather of the (M, N / g) output slices.
 
+`gather="fused"` removes that collective: the output buffer of every rank lives in symmetric memory (mapped into all processes of
+the node), and the GEMM of a rank writes its output columns into the full-width (M, N) buffer of every rank from its tile epilogue (one
+TMA store per destination and 32 x 32 block of outputs, over NVLink for the peers), so the transfer runs under the tensor-core work
+tile by tile.  Nothing is ever loaded from a peer.  Two small NCCL all-reduces order the step against the readers on the other ranks.
+
 Whether sharding pays is a property of the shape: the GEMM shrinks by g but every rank must receive (g - 1) / g of the (M, N) output,
 so `worth_sharding()` compares the two and `ShardedLinear` can keep the output sharded (`gather=None`) for a consumer that is sharded
 the same way (attention heads of a fused QKV projection).
@@ -63,6 +68,7 @@ class ShardedLinear:
             from wgpkernels_b200 import int8
             self.linear = int8.linear
         self._gathered = None
+        self._symmetric = {}  # (M, dtype) -> (own buffer, views of every rank's buffer, barrier token)
 
     @classmethod
     def from_full(cls, weight, scale, bias=None, group=None, linear=None):
@@ -77,11 +83,43 @@ class ShardedLinear:
         """This rank's output columns (M, N_local).  residual / residual_scale: the rank's own columns."""
         return self.linear(x, self.weight, self.scale, self.bias, residual=residual, residual_scale=residual_scale, **kwargs)
 
+    def symmetric_output(self, m, dtype, device):
+        """(own (M, N) buffer, [view of rank r's buffer for every r], token) in symmetric memory; a collective call the first time."""
+        key = (m, dtype)
+        if key not in self._symmetric:
+            import torch.distributed._symmetric_memory as symmetric_memory
+            own = symmetric_memory.empty((m, self.n_total), dtype=dtype, device=device)
+            handle = symmetric_memory.rendezvous(own, self.group if self.group is not None else dist.group.WORLD)
+            views = [own if r == self.rank else handle.get_buffer(r, (m, self.n_total), dtype) for r in range(self.world_size)]
+            self._symmetric[key] = (own, views, torch.zeros(1, device=device), handle)
+        return self._symmetric[key][:3]
+
+    def fused(self, x, residual=None, residual_scale=None, **kwargs):
+        """(M, N) on every rank, each rank's GEMM writing its columns into all ranks' buffers.  The result is this layer's own buffer for
+        (M, dtype): it is overwritten by the next call with the same M.  residual / residual_scale: the rank's own columns, (M, N / g)
+        with any row stride and (N / g)."""
+        own, views, token = self.symmetric_output(x.shape[0], x.dtype, x.device)
+        # every rank has finished reading the previous contents of the buffers (this rank's kernels that read them precede on its stream)
+        dist.all_reduce(token, group=self.group)
+        # own buffer first, then the peers starting from the next rank, so that the ranks do not all store to the same GPU at once
+        order = [(self.rank + d) % self.world_size for d in range(self.world_size)]
+        outputs = [views[r][:, self.start:self.stop] for r in order]
+        kwargs.pop("out", None)
+        self.linear(x, self.weight, self.scale, self.bias, residual=residual, residual_scale=residual_scale, out=outputs, **kwargs)
+        dist.all_reduce(token, group=self.group)  # every rank's stores have been issued and completed before anyone reads
+        return own
+
     def __call__(self, x, gather="full", broadcast_input=False, residual=None, residual_scale=None, **kwargs):
         """gather: 'full' -> (M, N) on every rank; 'blocked' -> (g, M, N / g), rank-major (what the all-gather delivers, no extra copy);
-        None -> the local (M, N / g) slice only.  broadcast_input: x is valid on rank 0 only and is broadcast first."""
+        'fused' -> (M, N) on every rank without a collective on the data (see fused(); block / exact / row paths only);
+        None -> the local (M, N / g) slice only.  residual / residual_scale: the rank's own columns.
+        broadcast_input: x is valid on rank 0 only and is broadcast first."""
         if broadcast_input and self.world_size > 1:
             dist.broadcast(x, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0, group=self.group)
+        if gather == "fused" and self.world_size > 1:
+            return self.fused(x, residual=residual, residual_scale=residual_scale, **kwargs)
+        if gather == "fused":
+            gather = "full"
         y = self.local(x, residual=residual, residual_scale=residual_scale, **kwargs)
         if gather is None or self.world_size == 1:
             return y if gather != "blocked" else y.unsqueeze(0)

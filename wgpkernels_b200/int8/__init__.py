@@ -82,6 +82,7 @@ def load_library(path=None):
     lib.wq8_gemm.argtypes = [p, p, p, p, p, p, p, p, p, i, i, i, i, i, i, i, p, p, p]
     lib.wq8_gemm_workspace.argtypes = [i, i, i, i, i, i, p]
     lib.wq8_gemm_workspace.restype = None
+    lib.wq8_gemm_multi.argtypes = [p, p, p, p, p, p, p, i64, p, p, i, i64, i, i, i, i, i, i, p, p]
     lib.wq8_gemm_select.argtypes = [i, i, i, i, i]
     lib.wq8_small.argtypes = [p, i64, p, p, p, p, p, p, i, i, i, i, i, p, p, p]
     lib.wq8_small_workspace.argtypes = [i, i, i, i, p]
@@ -364,7 +365,9 @@ def _weight_scale_groups(sb):
 def gemm(a, a_lo, sa, b, sb, bias, out_dtype, split=None, variant=None, out=None, mode=None, residual=None, residual_scale=None):
     """INT8 x INT8 GEMM with the fused epilogue.  mode: 'row' (sa per row), 'exact' (a_lo given) or 'block' (sa per row and 128-element
     block); inferred when omitted.  sb: (N) per channel, or (N, ceil(K / 128)) with 'exact' / 'block'.  residual (M, N) and residual_scale (N)
-    in out_dtype: Y = residual + residual_scale * (A @ B.T + bias); out may be the residual."""
+    in out_dtype: Y = residual + residual_scale * (A @ B.T + bias); out may be the residual.  out and residual may be column ranges of wider
+    matrices (unit column stride, row stride a multiple of 8); out may also be a list of up to 8 such (M, N) views of equal row stride,
+    which all receive the output (the ranks' buffers of an N-sharded layer, the peers' ones mapped into this process)."""
     lib = _require()
     m, k = a.shape
     n = b.shape[0]
@@ -373,14 +376,27 @@ def gemm(a, a_lo, sa, b, sb, bias, out_dtype, split=None, variant=None, out=None
     if out_dtype not in (torch.float16, torch.bfloat16):
         raise ValueError("the output dtype must be float16 or bfloat16")
     sms = _sm_count(a.device)
-    y = torch.empty((m, n), dtype=out_dtype, device=a.device) if out is None else out
+    targets = list(out) if isinstance(out, (list, tuple)) else None
+    y = torch.empty((m, n), dtype=out_dtype, device=a.device) if out is None else targets[0] if targets else out
+    strided = targets is not None or y.stride(0) != n or (residual is not None and residual.stride(0) != n)
+    if strided:
+        targets = targets or [y]
+        if not 1 <= len(targets) <= 8:
+            raise ValueError("between 1 and 8 outputs")
+        for t in targets:
+            if tuple(t.shape) != (m, n) or t.dtype != out_dtype or t.stride(1) != 1 or t.stride(0) != y.stride(0):
+                raise ValueError("every output must be an (M, N) view of the output dtype with unit column stride and the same row stride")
+        if residual is not None and (tuple(residual.shape) != (m, n) or residual.stride(1) != 1):
+            raise ValueError("the residual must be an (M, N) view with unit column stride")
     if variant is None and split is None:
         mode = mode or ("exact" if a_lo is not None else "block" if sa.dim() == 2 else "row")
         if _weight_scale_groups(sb):
             if mode == "row":
                 raise ValueError("Weights with per-(n, k-block) scales run the 'block' or 'exact' path")
             mode += "+g"
-        variant, split, workspace_bytes, counter_bytes = _plan(a, a_lo, sa, b, sb, bias, y, mode, residual is not None)
+        tuning_y = torch.empty((m, n), dtype=out_dtype, device=a.device) if strided else y  # the tuner may overwrite its output
+        variant, split, workspace_bytes, counter_bytes = _plan(a, a_lo, sa, b, sb, bias, tuning_y, mode, residual is not None and not strided)
+        del tuning_y
     else:
         split = 1 if split is None else split
         lib.wq8_gemm_workspace(m, n, k, variant, sms, split, _sizes)
@@ -388,6 +404,12 @@ def gemm(a, a_lo, sa, b, sb, bias, out_dtype, split=None, variant=None, out=None
     workspace = torch.empty(workspace_bytes, dtype=torch.uint8, device=a.device) if workspace_bytes else None
     stream = _stream(a.device)
     counters = _zeroed_counters(a.device, counter_bytes, stream).data_ptr() if counter_bytes else None
+    if strided:
+        pointers = (ctypes.c_void_p * len(targets))(*[t.data_ptr() for t in targets])
+        _check(lib.wq8_gemm_multi(a.data_ptr(), _ptr(a_lo), sa.data_ptr(), b.data_ptr(), sb.data_ptr(), _ptr(bias), _ptr(residual),
+                                  residual.stride(0) if residual is not None else 0, _ptr(residual_scale), pointers, len(targets), y.stride(0),
+                                  m, n, k, _DTYPES[out_dtype], variant, sms, _ptr(workspace), stream))
+        return y
     _check(lib.wq8_gemm(a.data_ptr(), _ptr(a_lo), sa.data_ptr(), b.data_ptr(), sb.data_ptr(), _ptr(bias), _ptr(residual), _ptr(residual_scale),
                         y.data_ptr(), m, n, k, _DTYPES[out_dtype], variant, sms, split, _ptr(workspace), counters, stream))
     return y
@@ -450,7 +472,8 @@ def _gemm_path(x, weight, scale, bias, group, mode, act=None, act_weight=None, e
     for start in range(0, m, rows):
         stop = min(start + rows, m)
         prepared = prepare(x[start:stop], group, mode, act, act_weight, eps)
-        linear_prepared(prepared, weight, scale, bias, None if residual is None else residual[start:stop], residual_scale, out[start:stop])
+        rows_out = [t[start:stop] for t in out] if isinstance(out, (list, tuple)) else out[start:stop]
+        linear_prepared(prepared, weight, scale, bias, None if residual is None else residual[start:stop], residual_scale, rows_out)
         del prepared
     return out
 
