@@ -37,6 +37,8 @@ def test_lines(wq, shape, residual, dtype):
     assert rel(y, expected) < 1e-3
     y_ref = reflib.gemv_lines(gx, gw, gsw, gbias, gres, grs)
     assert rel(y, y_ref) < 1e-3
+    assert torch.equal(y, wq.gemv_lines(gx, gw, gsw, gbias, gres, grs))  # fixed-order reductions: run to run identical
+    assert wq.debug_status() == 0
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
@@ -55,6 +57,7 @@ def test_small(wq, shape, residual, dtype):
     assert torch.equal(y, wq.small(gx, gw, gsw, gbias, gres, grs))  # fixed-order reductions: run to run identical
     # the split-K counters are left zeroed
     assert not wq._counters[0].any().item()
+    assert wq.debug_status() == 0
 
 
 def test_small_in_place_residual(wq):

@@ -1,5 +1,6 @@
 // Shared device helpers of the INT8 weight-linear library (sm_100a).
 #pragma once
+#include <cuda.h>  // CUtensorMap and its enums only; cuTensorMapEncodeTiled is resolved through the runtime, libcuda is not linked
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
@@ -192,6 +193,11 @@ template <int GROUP> WQ_DEVICE void rotate_chunk(float* v) {
 template <int GROUP> __host__ __device__ constexpr float group_norm() { return GROUP == 256 ? 0.0625f : GROUP == 64 ? 0.125f : GROUP == 16 ? 0.25f : 1.f; }
 
 // ---- device status word (bounded waits report here instead of trapping) ----------------------------------------------
+// gemm_tc.cu: tensor map of a (rows, row_bytes) row-major byte matrix with boxes of box_rows rows x box_bytes bytes (at most 256), no
+// swizzle, zero fill outside; false when the driver entry point is missing or refuses the description.
+bool make_byte_matrix_map(CUtensorMap* map, const void* base, int rows, int row_bytes, int box_bytes, int box_rows);
+int stream_status_take();  // stream.cu: status of the weight-streaming kernels on the current device (0 = fine), cleared by the call
+
 enum Status : int { kOk = 0, kTimeoutFull = 1, kTimeoutEmpty = 2, kTimeoutTmemFull = 3, kTimeoutTmemEmpty = 4, kTimeoutScales = 5, kTimeoutParams = 6, kStatusSharedAlignment = 7 };
 
 }  // namespace wq

@@ -918,6 +918,17 @@ __global__ void regroup_weight_scales(const float* __restrict__ sb, float* __res
 constexpr int kScalePad = 256;
 static int padded_n(int n) { return (n + kScalePad - 1) / kScalePad * kScalePad; }
 
+bool make_byte_matrix_map(CUtensorMap* map, const void* base, int rows, int row_bytes, int box_bytes, int box_rows) {
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {cuuint64_t(row_bytes), cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(row_bytes)};
+    const cuuint32_t box[2] = {cuuint32_t(box_bytes), cuuint32_t(box_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 struct GemmArgs {
     float* scale_scratch;  // group-scaled weights: (ceil(K/128), padded_n(N)) floats of caller workspace
     const int8_t* a;
@@ -1104,5 +1115,7 @@ WQ_API int wq8_debug_status() {
     if (cudaMemcpyFromSymbol(&code, g_status, sizeof(int)) != cudaSuccess) return -1;
     const int zero = 0;
     cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
-    return code;
+    const int streaming = wq::stream_status_take();  // the weight-streaming kernels keep their own word
+    if (streaming < 0) return -1;
+    return code ? code : streaming ? 100 + streaming : 0;
 }

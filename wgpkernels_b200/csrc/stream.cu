@@ -169,6 +169,262 @@ __global__ void __launch_bounds__(256) stream_mma(const T* __restrict__ x, int64
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// stream_bulk: the same linear with the weights fed by the copy engine.
+//
+// stream_mma keeps at most 4 KiB per warp in flight and only while the warp is not computing; with one or two CTAs per SM that is far
+// from the bytes the HBM needs outstanding.  Here every warp owns a ring of kBulkStages stages of 4 KiB in shared memory, filled by
+// the TMA unit (one cp.async.bulk.tensor box of ROWS weight rows x 128 or 256 bytes of K per stage, no multicast, completion counted by
+// an mbarrier per stage; rows past N and bytes past K arrive as zeros): 16 warps x 3 stages x 4 KiB = 192 KiB per SM are requested
+// before any of it is needed, whatever the warps are doing.  One persistent CTA per SM walks work items of ROWS output channels (8, 16
+// or 32); the 16 warps of the CTA take the item's K segments in turn, the ring running ahead across item boundaries; a 17th warp adds
+// the partial sums of the 16 in warp order from shared memory (deterministic), scales, biases and stores them while the others are
+// already streaming the next item (two sets of partial sums, handed over through mbarriers).  No workspace of any kind.
+// Sixteen warps because the work per stage is a long dependent chain (activation loads, byte conversions, MMAs on one accumulator):
+// the SM needs that many chains in progress to keep issuing.
+// A wait that runs out (about a second of SM clocks) records a status code, the warp stops computing but keeps meeting the CTA's
+// mbarrier hand-overs (a warp that stopped no longer arrives, so its peers run out of time too), and the kernel ends with unspecified
+// output instead of hanging.  There is no CTA-wide barrier after the start.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int kBulkWarps = 16, kBulkThreads = 32 * (kBulkWarps + 1), kBulkPartials = 2;  // 16 streaming warps and the reducer warp
+constexpr long long kBulkWaitLimit = 2000000000ll;
+__device__ int g_stream_status = 0;
+
+WQ_DEVICE uint32_t bulk_smem_address(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+WQ_DEVICE bool bulk_stage_ready(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// false when the data did not arrive in time (recorded) or another warp of the CTA already gave up
+WQ_DEVICE bool bulk_wait(uint32_t bar, uint32_t parity, volatile int* gave_up) {
+    if (bulk_stage_ready(bar, parity)) return true;
+    const long long start = clock64();
+    for (uint32_t spin = 1;; ++spin) {
+        if (bulk_stage_ready(bar, parity)) return true;
+        if ((spin & 63u) == 0u) {
+            if (*gave_up) return false;
+            if (clock64() - start > kBulkWaitLimit) {
+                *gave_up = 1;
+                atomicCAS(&g_stream_status, 0, 1);
+                return false;
+            }
+        }
+    }
+}
+
+template <int MT, int ROWS> struct BulkShape {
+    static constexpr int kSegment = ROWS >= 32 ? 128 : 256;  // bytes of K per row and stage (a TMA box is at most 256 bytes wide)
+    static constexpr int kStageBytes = ROWS * kSegment;      // 2 KiB (8 rows) or 4 KiB
+    static constexpr int kSub = kSegment / kStreamChunk;     // 64-byte pieces per stage and row
+    static constexpr int kRowBlocks = ROWS >= 16 ? ROWS / 16 : 1;
+    // the partial sums of two items (one being reduced while the next is produced), then as many ring stages per warp as fit (at most 3)
+    static constexpr int kPartialBytes = kBulkPartials * kBulkWarps * MT * 8 * (ROWS + 1) * 4;
+    static constexpr int kRoom = (227 * 1024 - kPartialBytes - 1024) / (kBulkWarps * kStageBytes);
+    static constexpr int kStages = kRoom >= 3 ? 3 : kRoom;
+    static_assert(kStages >= 2, "the rings do not fit");
+    static constexpr int kRingBytes = kBulkWarps * kStages * kStageBytes;
+    static constexpr int kBarrierBytes = (kBulkWarps * kStages + 2 * kBulkPartials) * 8;
+    static constexpr int kSmemBytes = kRingBytes + kBarrierBytes + kPartialBytes + 16;
+};
+
+template <class T, int MT, int ROWS>
+__global__ void __launch_bounds__(kBulkThreads, 1) stream_bulk(const __grid_constant__ CUtensorMap map_w, const T* __restrict__ x, int64_t ldx, const float* __restrict__ sw,
+                                                      const T* __restrict__ bias, const T* residual, const T* __restrict__ rscale, T* y, int m, int n,
+                                                      int k) {
+    using S = BulkShape<MT, ROWS>;
+    constexpr int SEG = S::kSegment, SUB = S::kSub, RB = S::kRowBlocks, kStageBytes = S::kStageBytes, kStages = S::kStages;
+    constexpr bool kHalf = ROWS == 8;  // rows 8..15 of the MMA tile are empty
+    extern __shared__ __align__(1024) uint8_t bulk_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const uint32_t all_bars = bulk_smem_address(bulk_smem + S::kRingBytes);
+    const uint32_t sums_ready = all_bars + kBulkWarps * kStages * 8, sums_free = sums_ready + 8 * kBulkPartials;
+    using Partial = float[kBulkWarps][MT * 8][ROWS + 1];
+    Partial* partial = reinterpret_cast<Partial*>(bulk_smem + S::kRingBytes + S::kBarrierBytes);
+    volatile int* gave_up = reinterpret_cast<volatile int*>(bulk_smem + S::kRingBytes + S::kBarrierBytes + S::kPartialBytes);
+    if (threadIdx.x == 0) {
+        *gave_up = 0;
+        for (int s = 0; s < kBulkWarps * kStages; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(all_bars + 8 * s));
+        for (int s = 0; s < kBulkPartials; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sums_ready + 8 * s), "r"(kBulkWarps));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sums_free + 8 * s));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    }
+    __syncthreads();
+
+    const int items = (n + ROWS - 1) / ROWS, segments = (k + SEG - 1) / SEG;
+    const int my_items = int(blockIdx.x) < items ? (items - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;
+
+    if (warp == kBulkWarps) {
+        // ---------------- reducer: adds the 16 warps' partial sums of an item in warp order, scales, adds bias / residual, stores ----------------
+        bool ok = true;
+        for (int round = 0; round < my_items && ok; ++round) {
+            const int set = round % kBulkPartials;
+            if (!(ok = __all_sync(0xffffffffu, bulk_wait(sums_ready + 8 * set, uint32_t(round / kBulkPartials) & 1u, gave_up)))) break;
+            const int item = int(blockIdx.x) + round * int(gridDim.x);
+            for (int i = lane; i < MT * 8 * ROWS; i += 32) {
+                const int token = i / ROWS, r = i % ROWS, channel = item * ROWS + r;
+                if (token < m && channel < n) {
+                    float sum = 0.f;
+#pragma unroll
+                    for (int part = 0; part < kBulkWarps; ++part) sum += partial[set][part][token][r];
+                    float v = sum * sw[channel] + (bias ? as_float(bias[channel]) : 0.f);
+                    if (residual) v = fmaf(v, rscale ? as_float(rscale[channel]) : 1.f, as_float(residual[int64_t(token) * n + channel]));
+                    y[int64_t(token) * n + channel] = round_one<T>(v);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(sums_free + 8 * set) : "memory");
+        }
+        return;
+    }
+
+    // ---------------- streaming warps ----------------
+    uint8_t* ring = bulk_smem + warp * kStages * kStageBytes;
+    const uint32_t ring_address = bulk_smem_address(ring);
+    const uint32_t bars = all_bars + warp * kStages * 8;
+    const int per_item = warp < segments ? (segments - warp + kBulkWarps - 1) / kBulkWarps : 0;  // this warp's stages of one item
+    const long long total = (long long)my_items * per_item;
+
+    // stage number q of this warp: the rows of item (q / per_item) at K segment warp + 16 (q % per_item), into ring slot q % kStages
+    auto request = [&](long long q) {
+        const int item = int(blockIdx.x) + int(q / per_item) * int(gridDim.x), segment = warp + int(q % per_item) * kBulkWarps;
+        const int slot = int(q % kStages);
+        const uint32_t bar = bars + 8 * slot;
+        if (lane == 0) {
+            // the whole box is counted, zero-filled parts included
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kStageBytes) : "memory");
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                             ring_address + slot * kStageBytes),
+                         "l"(&map_w), "r"(bar), "r"(segment * SEG), "r"(item * ROWS)
+                         : "memory");
+        }
+    };
+
+    const T* x_row[MT];
+    bool x_ok[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        const int token = mt * 8 + g;
+        x_ok[mt] = token < m;
+        x_row[mt] = x + int64_t(x_ok[mt] ? token : 0) * ldx + 16 * t;
+    }
+
+    long long requested = 0;
+    for (; requested < total && requested < kStages; ++requested) request(requested);
+    bool ok = true;
+    long long q = 0, landed = 0;
+    for (int round = 0; round < my_items; ++round) {
+        // with few outputs per lane, two chains of MMAs per output (even and odd 16-byte pieces) instead of one long dependent chain
+        constexpr bool kTwoChains = RB * MT <= 2;
+        float acc[RB][MT][4], odd[kTwoChains ? RB : 1][kTwoChains ? MT : 1][4];
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                acc[rb][mt][0] = acc[rb][mt][1] = acc[rb][mt][2] = acc[rb][mt][3] = 0.f;
+                if (kTwoChains) odd[rb][mt][0] = odd[rb][mt][1] = odd[rb][mt][2] = odd[rb][mt][3] = 0.f;
+            }
+        for (int j = 0; j < per_item; ++j, ++q) {
+            const int slot = int(q % kStages);
+            const int segment = warp + j * kBulkWarps;
+            const int pieces = min(SUB, (k - segment * SEG) / kStreamChunk);
+            // the activations of a piece: this lane's 16 values start at k0 + 16 t.  They do not depend on the stage: the first piece's are
+            // requested before the wait, every other piece's while the piece before it is multiplied.
+            uint4 xv[MT][2], ahead[MT][2];
+            auto fetch_x = [&](int u, uint4 (&v)[MT][2]) {
+                const int64_t k0 = int64_t(segment) * SEG + u * kStreamChunk;
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const T* p = x_row[mt] + k0;
+                    v[mt][0] = x_ok[mt] ? __ldg(reinterpret_cast<const uint4*>(p)) : make_uint4(0u, 0u, 0u, 0u);
+                    v[mt][1] = x_ok[mt] ? __ldg(reinterpret_cast<const uint4*>(p) + 1) : make_uint4(0u, 0u, 0u, 0u);
+                }
+            };
+            fetch_x(0, ahead);
+            if (ok) ok = __all_sync(0xffffffffu, bulk_wait(bars + 8 * slot, uint32_t(q / kStages) & 1u, gave_up));
+            if (ok) {
+                ++landed;
+                const uint8_t* stage = ring + slot * kStageBytes;
+#pragma unroll
+                for (int u = 0; u < SUB; ++u) {
+                    if (u < pieces) {
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            xv[mt][0] = ahead[mt][0];
+                            xv[mt][1] = ahead[mt][1];
+                        }
+                        if (u + 1 < pieces) fetch_x(u + 1, ahead);
+#pragma unroll
+                        for (int rb = 0; rb < RB; ++rb) {
+                            const uint4 row0 = *reinterpret_cast<const uint4*>(stage + (rb * 16 + g) * SEG + u * kStreamChunk + 16 * t);
+                            const uint4 row1 = kHalf ? make_uint4(0u, 0u, 0u, 0u)
+                                                     : *reinterpret_cast<const uint4*>(stage + (rb * 16 + g + 8) * SEG + u * kStreamChunk + 16 * t);
+                            const uint32_t* r0 = reinterpret_cast<const uint32_t*>(&row0);
+                            const uint32_t* r1 = reinterpret_cast<const uint32_t*>(&row1);
+#pragma unroll
+                            for (int piece = 0; piece < 4; ++piece) {
+                                uint32_t a0, a1 = 0u, a2, a3 = 0u;
+                                int8x4_to_pairs<T>(r0[piece], a0, a2);
+                                if (!kHalf) int8x4_to_pairs<T>(r1[piece], a1, a3);
+#pragma unroll
+                                for (int mt = 0; mt < MT; ++mt) {
+                                    const uint32_t* xs = reinterpret_cast<const uint32_t*>(&xv[mt][piece >> 1]);
+                                    float* chain = kTwoChains && (piece & 1) ? odd[kTwoChains ? rb : 0][kTwoChains ? mt : 0] : acc[rb][mt];
+                                    mma_16x8x16<T>(chain, a0, a1, a2, a3, xs[(piece & 1) * 2], xs[(piece & 1) * 2 + 1]);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();  // every lane has read the stage: its slot takes the stage kStages ahead
+            if (ok && requested < total) request(requested++);
+        }
+        // hand the item's partial sums to the reducer: the set of this round is free once the reducer has finished the round two before
+        const int set = round % kBulkPartials;
+        if (ok && round >= kBulkPartials)
+            ok = __all_sync(0xffffffffu, bulk_wait(sums_free + 8 * set, uint32_t(round / kBulkPartials - 1) & 1u, gave_up));
+        // acc[rb][mt] = {(row g, token 2t), (g, 2t + 1), (g + 8, 2t), (g + 8, 2t + 1)} of row block rb and token block mt
+        if (ok) {
+#pragma unroll
+            for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (kTwoChains) acc[rb][mt][e] += odd[kTwoChains ? rb : 0][kTwoChains ? mt : 0][e];
+                    partial[set][warp][mt * 8 + 2 * t][rb * 16 + g] = acc[rb][mt][0];
+                    partial[set][warp][mt * 8 + 2 * t + 1][rb * 16 + g] = acc[rb][mt][1];
+                    if (!kHalf) {
+                        partial[set][warp][mt * 8 + 2 * t][rb * 16 + g + 8] = acc[rb][mt][2];
+                        partial[set][warp][mt * 8 + 2 * t + 1][rb * 16 + g + 8] = acc[rb][mt][3];
+                    }
+                }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(sums_ready + 8 * set) : "memory");
+        }
+    }
+    // A warp that gave up may still have copies on their way into its ring: give them a bounded chance to land before the CTA's shared
+    // memory goes away.
+    if (!ok) {
+        for (long long pending = landed; pending < requested; ++pending) {
+            const long long start = clock64();
+            while (!bulk_stage_ready(bars + 8 * int(pending % kStages), uint32_t(pending / kStages) & 1u) && clock64() - start < kBulkWaitLimit / 8) {}
+        }
+    }
+}
+
 // General GEMV for one to four tokens when the tensor-core kernel's alignment does not hold (K multiple of 4 only, rows of x 8-byte
 // aligned): a warp per output channel, four weight bytes per lane and step, exact INT8 -> FP32 conversion, FP32 FMA, butterfly sum.
 template <class T, int ROWS>
@@ -261,6 +517,78 @@ static int launch_cores(const void* x, int64_t ldx, const int8_t* w, const float
     return int(cudaGetLastError());
 }
 
+// Rows per work item of stream_bulk (0: the shape is left to stream_mma).  More rows per item read the activations fewer times (every
+// item reads all of x from L2) and reduce less often; fewer rows balance the items over the SMs better.
+static int plan_bulk(int m, int n, int k, int sms) {
+    if (sms <= 0) sms = 148;
+    int best = 0;
+    double best_score = 0.0;
+    for (int rows = 8; rows <= 32; rows *= 2) {
+        const int segment = rows >= 32 ? 128 : 256;
+        if (k / segment < kBulkWarps) continue;  // fewer K segments than warps: warps would idle
+        if (rows == 32 && m > 16) continue;        // two sets of partial sums of 32 rows x 32 tokens x 16 warps do not fit beside the rings
+        const int items = (n + rows - 1) / rows, rounds = (items + sms - 1) / sms;
+        const double balance = double(items) / (double(sms) * rounds), activations = 1.0 + 0.3 * 2.0 * m / rows;
+        const double score = balance / activations * (1.0 + 0.0005 * rows);  // ties go to the larger item
+        if (score > best_score) {
+            best_score = score;
+            best = rows;
+        }
+    }
+    return best;
+}
+
+template <class T, int MT, int ROWS>
+static int launch_bulk_shape(const T* x, int64_t ldx, const int8_t* w, const float* sw, const T* bias, const T* residual, const T* rscale, T* y, int m,
+                             int n, int k, int sms, cudaStream_t stream) {
+    using S = BulkShape<MT, ROWS>;
+    auto kernel = stream_bulk<T, MT, ROWS>;
+    static bool configured[64] = {};  // the attribute belongs to a device's copy of the kernel
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device < 0 || device >= 64 || !configured[device]) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes);
+        if (e != cudaSuccess) return int(e);
+        if (device >= 0 && device < 64) configured[device] = true;
+    }
+    CUtensorMap map_w;
+    if (!make_byte_matrix_map(&map_w, w, n, k, S::kSegment, ROWS)) return int(cudaErrorNotSupported);
+    const int items = (n + ROWS - 1) / ROWS;
+    kernel<<<items < sms ? items : sms, kBulkThreads, S::kSmemBytes, stream>>>(map_w, x, ldx, sw, bias, residual, rscale, y, m, n, k);
+    return int(cudaGetLastError());
+}
+
+template <class T>
+static int launch_bulk(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale, void* y,
+                       int m, int n, int k, int rows, int sms, cudaStream_t stream) {
+    auto xs = static_cast<const T*>(x);
+    auto b = static_cast<const T*>(bias), r = static_cast<const T*>(residual), rs = static_cast<const T*>(rscale);
+    auto out = static_cast<T*>(y);
+    if (sms <= 0) sms = 148;
+#define WQ_BULK(MT, ROWS) return launch_bulk_shape<T, MT, ROWS>(xs, ldx, w, sw, b, r, rs, out, m, n, k, sms, stream)
+    switch (tokens_blocks(m) * 100 + rows) {
+        case 108: WQ_BULK(1, 8);
+        case 116: WQ_BULK(1, 16);
+        case 132: WQ_BULK(1, 32);
+        case 208: WQ_BULK(2, 8);
+        case 216: WQ_BULK(2, 16);
+        case 232: WQ_BULK(2, 32);
+        case 408: WQ_BULK(4, 8);
+        case 416: WQ_BULK(4, 16);
+    }
+#undef WQ_BULK
+    return -2;
+}
+
+// Status of the streaming kernels on the current device: 0, or 1 when a wait for weight data gave up; clears it.
+int stream_status_take() {
+    int code = 0;
+    const int zero = 0;
+    if (cudaMemcpyFromSymbol(&code, g_stream_status, sizeof(int)) != cudaSuccess) return -1;
+    if (code) cudaMemcpyToSymbol(g_stream_status, &zero, sizeof(int));
+    return code;
+}
+
 static int device_sms() {
     int device = 0, sms = 148;
     cudaGetDevice(&device);
@@ -284,6 +612,11 @@ WQ_API int wq8_small(const void* x, int64_t ldx, const int8_t* w, const float* s
     if (m <= 0 || n <= 0) return 0;
     if (k <= 0 || k % 64 || m > 32 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return -2;
     if (dtype != 0 && dtype != 1) return -1;
+    if ((reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+        const int rows = plan_bulk(m, n, k, sms);
+        if (rows && dtype == 0) return launch_bulk<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
+        if (rows) return launch_bulk<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
+    }
     StreamPlan p = plan_stream(n, k, sms, true);
     if (p.splits > 1 && (!slots || !counters)) p.splits = 1;
     if (dtype == 0) return launch_stream<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, slots, counters, stream);
@@ -297,7 +630,10 @@ WQ_API int wq8_gemv_lines(const void* x, int64_t ldx, const int8_t* w, const flo
     if (dtype != 0 && dtype != 1) return -1;
     const bool tensor_cores = k % 64 == 0 && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
     if (tensor_cores) {
-        const StreamPlan p = plan_stream(n, k, device_sms(), false);
+        const int sms = device_sms(), rows = plan_bulk(m, n, k, sms);
+        if (rows && dtype == 0) return launch_bulk<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
+        if (rows) return launch_bulk<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
+        const StreamPlan p = plan_stream(n, k, sms, false);
         if (dtype == 0) return launch_stream<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, nullptr, nullptr, stream);
         return launch_stream<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, nullptr, nullptr, stream);
     }
