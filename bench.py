@@ -158,6 +158,19 @@ def run_few_tokens(args, rank):
         marks.append((first, last))
     torch.cuda.synchronize()
     times = [first.elapsed_time(last) for first, last in marks]
+    # The same bytes read by a plain streaming kernel (the library's flush kernel on the cold start of its own buffer), timed the same
+    # way: what a launch of this size can reach at all.  A 60-120 MB read lasts 10-20 us at the HBM rate, so launch, ramp-up and tail
+    # are a large part of any such launch.
+    probe_marks = []
+    for _ in range(args.steps):
+        wq._check(lib.wq8_l2_flush(0, flush_bytes, stream))
+        first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        first.record()
+        wq._check(lib.wq8_l2_flush(0, c.n * c.k, stream))
+        last.record()
+        probe_marks.append((first, last))
+    torch.cuda.synchronize()
+    probe_ms = sorted(first.elapsed_time(last) for first, last in probe_marks)[len(probe_marks) // 2]
     lib.wq8_l2_flush_release()
     clocks = sampler.stop()
     ms = sorted(times)[len(times) // 2]
@@ -175,7 +188,9 @@ def run_few_tokens(args, rank):
                                             "l2": "flushed before every timed launch (read of 8 x L2 bytes)"},
             "effective_tops": 2 * m * n * k / (ms * 1e-3) / 1e12, "gpu_launches": args.steps * (2 if c.act or path == "exact" else 1), "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                         "algorithmic_bytes": moved, "peak_source": "MEASURED_PEAKS hbm_gbs, of measured" if peaks else "of fallback"}}
+                         "algorithmic_bytes": moved, "peak_source": "MEASURED_PEAKS hbm_gbs, of measured" if peaks else "of fallback",
+                         "plain_read": {"ms": probe_ms, "gbs": c.n * c.k / (probe_ms * 1e-3) / 1e9, "frac_of_it": probe_ms / ms * moved / (c.n * c.k),
+                                        "what": "a plain read kernel over the weight's byte count, cold, same events"}}}
     print(json.dumps(line), flush=True)
 
 

@@ -116,6 +116,15 @@ int wq8_gemm_multi(const int8_t* a, const int8_t* a_lo, const float* sa, const i
                    const void* residual, int64_t ld_residual, const void* rscale, void* const* ys, int count, int64_t ld_y, int m, int n, int k,
                    int dtype, int variant, int sms, int* workspace, wq8_stream_t stream);
 
+/* The few-token linear (at most 8 tokens, K multiple of 128) on INT8 tensor cores with the weights as they are: the activations are
+ * first split into three planes of signed 7-bit digits per 128 values with one power of two (exact for every value within 2^14 of the
+ * largest of its 128), into `workspace` (wq8_stream_planes_workspace() bytes, 16-byte aligned; 0 = the shape is not supported, use
+ * wq8_gemv_lines / wq8_small).  Same arguments and error codes as wq8_small otherwise.  The reference has no counterpart: its few-token
+ * kernels (and wq8_gemv_lines / wq8_small here) convert every weight byte to BF16 / FP16 instead, which bounds them below the HBM rate. */
+int64_t wq8_stream_planes_workspace(int m, int n, int k, int sms);
+int wq8_stream_planes(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
+                      void* y, int m, int n, int k, int dtype, int sms, void* workspace, wq8_stream_t stream);
+
 /* wq8_small for callers that cannot allocate device memory (no counterpart in the reference, which always takes caller scratch).
  * A host that reaches this library through a bare FFI with buffers it was handed, a serving loop under a fixed memory budget, code
  * running during CUDA graph capture or in a section where cudaMalloc is not allowed: none of them can supply the K-split scratch

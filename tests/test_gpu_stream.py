@@ -25,10 +25,19 @@ def cuda(*tensors):
     return [None if t is None else t.cuda() for t in tensors]
 
 
+@pytest.fixture(params=["planes", "converted"])
+def kernel(request, wq, monkeypatch):
+    """Both few-token kernels for shapes of at most 8 tokens: 'planes' (activations as INT8 digit planes, the Python module's choice) and
+    'converted' (weights converted to the activation type: what wq8_gemv_lines / wq8_small of the C ABI run, and every larger shape)."""
+    if request.param == "converted":
+        monkeypatch.setattr(wq, "_stream_planes", lambda *args: False)
+    return request.param
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
 @pytest.mark.parametrize("residual", [False, True], ids=["plain", "residual"])
 @pytest.mark.parametrize("shape", [(1, 96, 256), (2, 100, 260), (3, 4096, 1024), (4, 520, 4096 + 64), (4, 28672, 4096), (1, 4096, 14336)], ids=str)
-def test_lines(wq, shape, residual, dtype):
+def test_lines(wq, kernel, shape, residual, dtype):
     m, n, k = shape
     x, w, sw, bias, res, rs = case(m, n, k, dtype, 101, residual)
     gx, gw, gsw, gbias, gres, grs = cuda(x, w, sw, bias, res, rs)
@@ -45,7 +54,7 @@ def test_lines(wq, shape, residual, dtype):
 @pytest.mark.parametrize("residual", [False, True], ids=["plain", "residual"])
 @pytest.mark.parametrize("shape", [(5, 96, 256), (8, 1000, 1024), (16, 28672, 4096), (16, 4096, 14336), (32, 4096, 14336), (32, 1024, 8192), (9, 40, 64),
                                    (24, 2048, 4096)], ids=str)
-def test_small(wq, shape, residual, dtype):
+def test_small(wq, kernel, shape, residual, dtype):
     m, n, k = shape
     x, w, sw, bias, res, rs = case(m, n, k, dtype, 111, residual)
     gx, gw, gsw, gbias, gres, grs = cuda(x, w, sw, bias, res, rs)
@@ -76,3 +85,19 @@ def test_strided_activation(wq):
     sw = torch.full((256,), 0.001).cuda()
     assert torch.equal(wq.gemv_lines(x, w, sw), wq.gemv_lines(x.contiguous(), w, sw))
     assert torch.equal(wq.small(x, w, sw), wq.small(x.contiguous(), w, sw))
+
+
+def test_planes_keep_small_values_next_to_large_ones(wq):
+    """The digit planes share one power of two per 128 values: values down to 2^-14 of the largest of their run are exact, so a run that
+    mixes 1000.0 with values around 0.5 still gives the FP32 result."""
+    m, n, k = 4, 512, 4096
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16)
+    x[:, ::128] = 1000.0
+    w = rand_int8((n, k), 6)
+    w[:, ::128] = 0  # the large values do not contribute: the result is made of the small ones only
+    sw = torch.full((n,), 0.001)
+    y = wq.gemv_lines(x.cuda(), w.cuda(), sw.cuda())
+    expected = (x.double() @ w.double().T * 0.001).to(torch.bfloat16)
+    assert rel(y, expected) < 2e-3
+    assert wq.debug_status() == 0

@@ -296,10 +296,14 @@ __global__ void __launch_bounds__(kBulkThreads, 1) stream_bulk(const __grid_cons
     const int per_item = warp < segments ? (segments - warp + kBulkWarps - 1) / kBulkWarps : 0;  // this warp's stages of one item
     const long long total = (long long)my_items * per_item;
 
-    // stage number q of this warp: the rows of item (q / per_item) at K segment warp + 16 (q % per_item), into ring slot q % kStages
-    auto request = [&](long long q) {
-        const int item = int(blockIdx.x) + int(q / per_item) * int(gridDim.x), segment = warp + int(q % per_item) * kBulkWarps;
-        const int slot = int(q % kStages);
+    // the next stage to request: the rows of this CTA's item number ask_round at the warp's K segment number ask_j, into ring slot ask_slot
+    // (plain counters: a division per stage would cost more instructions than the stage's arithmetic)
+    int ask_round = 0, ask_j = 0, ask_slot = 0;
+    auto request = [&]() {
+        const int item = int(blockIdx.x) + ask_round * int(gridDim.x), segment = warp + ask_j * kBulkWarps;
+        const int slot = ask_slot;
+        if (++ask_j == per_item) { ask_j = 0; ++ask_round; }
+        if (++ask_slot == kStages) ask_slot = 0;
         const uint32_t bar = bars + 8 * slot;
         if (lane == 0) {
             // the whole box is counted, zero-filled parts included
@@ -321,9 +325,11 @@ __global__ void __launch_bounds__(kBulkThreads, 1) stream_bulk(const __grid_cons
     }
 
     long long requested = 0;
-    for (; requested < total && requested < kStages; ++requested) request(requested);
+    for (; requested < total && requested < kStages; ++requested) request();
     bool ok = true;
-    long long q = 0, landed = 0;
+    long long landed = 0;
+    int slot = 0;
+    uint32_t parity = 0;  // of the stage the warp consumes next
     for (int round = 0; round < my_items; ++round) {
         // with few outputs per lane, two chains of MMAs per output (even and odd 16-byte pieces) instead of one long dependent chain
         constexpr bool kTwoChains = RB * MT <= 2;
@@ -335,8 +341,7 @@ __global__ void __launch_bounds__(kBulkThreads, 1) stream_bulk(const __grid_cons
                 acc[rb][mt][0] = acc[rb][mt][1] = acc[rb][mt][2] = acc[rb][mt][3] = 0.f;
                 if (kTwoChains) odd[rb][mt][0] = odd[rb][mt][1] = odd[rb][mt][2] = odd[rb][mt][3] = 0.f;
             }
-        for (int j = 0; j < per_item; ++j, ++q) {
-            const int slot = int(q % kStages);
+        for (int j = 0; j < per_item; ++j) {
             const int segment = warp + j * kBulkWarps;
             const int pieces = min(SUB, (k - segment * SEG) / kStreamChunk);
             // the activations of a piece: this lane's 16 values start at k0 + 16 t.  They do not depend on the stage: the first piece's are
@@ -352,7 +357,7 @@ __global__ void __launch_bounds__(kBulkThreads, 1) stream_bulk(const __grid_cons
                 }
             };
             fetch_x(0, ahead);
-            if (ok) ok = __all_sync(0xffffffffu, bulk_wait(bars + 8 * slot, uint32_t(q / kStages) & 1u, gave_up));
+            if (ok) ok = __all_sync(0xffffffffu, bulk_wait(bars + 8 * slot, parity, gave_up));
             if (ok) {
                 ++landed;
                 const uint8_t* stage = ring + slot * kStageBytes;
@@ -389,7 +394,11 @@ __global__ void __launch_bounds__(kBulkThreads, 1) stream_bulk(const __grid_cons
                 }
             }
             __syncwarp();  // every lane has read the stage: its slot takes the stage kStages ahead
-            if (ok && requested < total) request(requested++);
+            if (ok && requested < total) {
+                request();
+                ++requested;
+            }
+            if (++slot == kStages) { slot = 0; parity ^= 1u; }
         }
         // hand the item's partial sums to the reducer: the set of this round is free once the reducer has finished the round two before
         const int set = round % kBulkPartials;
@@ -420,7 +429,237 @@ __global__ void __launch_bounds__(kBulkThreads, 1) stream_bulk(const __grid_cons
     if (!ok) {
         for (long long pending = landed; pending < requested; ++pending) {
             const long long start = clock64();
-            while (!bulk_stage_ready(bars + 8 * int(pending % kStages), uint32_t(pending / kStages) & 1u) && clock64() - start < kBulkWaitLimit / 8) {}
+            while (!bulk_stage_ready(bars + 8 * int(pending % kStages), uint32_t(pending / kStages) & 1u) && clock64() - start < kBulkWaitLimit / 8) {
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// stream_planes: at most 8 tokens, INT8 tensor cores on the weights as they are.
+//
+// stream_bulk spends most of its instructions turning weight bytes into BF16 / FP16 (8 instructions per 4 bytes): at 1-8 tokens that,
+// not the HBM, bounds it.  Here the few activations are rewritten instead, once per call by split_planes: every run of 128 values of a
+// token becomes three planes of signed 7-bit digits with one power of two, x = 2^(E-7) (q0 + q1 / 128 + q2 / 16384), exact for every
+// value within 2^14 of the largest of its run (a BF16 / FP16 value has at most 11 significant bits; smaller values are truncated below
+// 2^-21 of the run's largest).  The weights then go into mma.sync.m16n8k32.s8 untouched: per plane an exact INT32 dot product over the
+// run, combined and scaled in FP32.  Same rings, reducer and hand-overs as stream_bulk.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int kPlaneRun = 128;   // values sharing one power of two
+constexpr int kPlaneTokens = 8;  // token slots of the planes (one MMA column block); unused ones hold zeros
+
+// planes: (8 tokens, 3, K) int8, scales: (K / 128, 8 tokens) float = 2^(E-7).  One warp per token and run, 4 values per lane.
+template <class T>
+__global__ void __launch_bounds__(256) split_planes(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ planes, float* __restrict__ scales, int m,
+                                                    int k) {
+    const int lane = threadIdx.x & 31, runs = k / kPlaneRun;
+    const int unit = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (unit >= runs * kPlaneTokens) return;
+    const int token = unit % kPlaneTokens, run = unit / kPlaneTokens;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (token < m) {
+        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + int64_t(token) * ldx + run * kPlaneRun + 4 * lane));
+        unpack_pair<T>(raw.x, v[0], v[1]);
+        unpack_pair<T>(raw.y, v[2], v[3]);
+    }
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    // amax < 2^E; the digits of v / 2^E in base 128, truncating toward zero (every remainder keeps the sign and is exact in FP32)
+    int exponent = 0;
+    if (amax > 0.f) frexpf(amax, &exponent);
+    exponent = max(exponent, -110);  // 2^(7 - E) and 2^(E - 7) stay finite, normal numbers; runs of denormal-sized values become zeros
+    const float down = ldexpf(1.f, 7 - exponent);
+    uint32_t packed[3] = {0u, 0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float f = v[j] * down;  // |f| < 128
+#pragma unroll
+        for (int p = 0; p < 3; ++p) {
+            const float digit = truncf(f);
+            packed[p] |= (uint32_t(int(digit)) & 0xffu) << (8 * j);
+            f = (f - digit) * 128.f;
+        }
+    }
+#pragma unroll
+    for (int p = 0; p < 3; ++p)
+        *reinterpret_cast<uint32_t*>(planes + (int64_t(token) * 3 + p) * k + run * kPlaneRun + 4 * lane) = packed[p];
+    if (lane == 0) scales[run * kPlaneTokens + token] = amax > 0.f ? ldexpf(1.f, exponent - 7) : 0.f;
+}
+
+WQ_DEVICE void mma_s8_16x8x32(int* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <class T, int ROWS>
+__global__ void __launch_bounds__(kBulkThreads, 1) stream_planes(const __grid_constant__ CUtensorMap map_w, const int8_t* __restrict__ planes,
+                                                                 const float* __restrict__ scales, const float* __restrict__ sw, const T* __restrict__ bias,
+                                                                 const T* residual, const T* __restrict__ rscale, T* y, int m, int n, int k) {
+    constexpr int MT = 1;
+    using S = BulkShape<MT, ROWS>;
+    constexpr int SEG = S::kSegment, RB = S::kRowBlocks, kStageBytes = S::kStageBytes, kStages = S::kStages;
+    constexpr int RUNS = SEG / kPlaneRun;  // runs of 128 values per stage: 2, or 1 with 32 rows
+    constexpr bool kHalf = ROWS == 8;
+    extern __shared__ __align__(1024) uint8_t bulk_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const uint32_t all_bars = bulk_smem_address(bulk_smem + S::kRingBytes);
+    const uint32_t sums_ready = all_bars + kBulkWarps * kStages * 8, sums_free = sums_ready + 8 * kBulkPartials;
+    using Partial = float[kBulkWarps][MT * 8][ROWS + 1];
+    Partial* partial = reinterpret_cast<Partial*>(bulk_smem + S::kRingBytes + S::kBarrierBytes);
+    volatile int* gave_up = reinterpret_cast<volatile int*>(bulk_smem + S::kRingBytes + S::kBarrierBytes + S::kPartialBytes);
+    if (threadIdx.x == 0) {
+        *gave_up = 0;
+        for (int s = 0; s < kBulkWarps * kStages; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(all_bars + 8 * s));
+        for (int s = 0; s < kBulkPartials; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sums_ready + 8 * s), "r"(kBulkWarps));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sums_free + 8 * s));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    }
+    __syncthreads();
+
+    const int items = (n + ROWS - 1) / ROWS, segments = (k + SEG - 1) / SEG;
+    const int my_items = int(blockIdx.x) < items ? (items - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;
+
+    if (warp == kBulkWarps) {
+        // ---------------- reducer (as in stream_bulk) ----------------
+        bool ok = true;
+        for (int round = 0; round < my_items && ok; ++round) {
+            const int set = round % kBulkPartials;
+            if (!(ok = __all_sync(0xffffffffu, bulk_wait(sums_ready + 8 * set, uint32_t(round / kBulkPartials) & 1u, gave_up)))) break;
+            const int item = int(blockIdx.x) + round * int(gridDim.x);
+            for (int i = lane; i < MT * 8 * ROWS; i += 32) {
+                const int token = i / ROWS, r = i % ROWS, channel = item * ROWS + r;
+                if (token < m && channel < n) {
+                    float sum = 0.f;
+#pragma unroll
+                    for (int part = 0; part < kBulkWarps; ++part) sum += partial[set][part][token][r];
+                    float v = sum * sw[channel] + (bias ? as_float(bias[channel]) : 0.f);
+                    if (residual) v = fmaf(v, rscale ? as_float(rscale[channel]) : 1.f, as_float(residual[int64_t(token) * n + channel]));
+                    y[int64_t(token) * n + channel] = round_one<T>(v);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(sums_free + 8 * set) : "memory");
+        }
+        return;
+    }
+
+    // ---------------- streaming warps ----------------
+    uint8_t* ring = bulk_smem + warp * kStages * kStageBytes;
+    const uint32_t ring_address = bulk_smem_address(ring);
+    const uint32_t bars = all_bars + warp * kStages * 8;
+    const int per_item = warp < segments ? (segments - warp + kBulkWarps - 1) / kBulkWarps : 0;
+    const long long total = (long long)my_items * per_item;
+    int ask_round = 0, ask_j = 0, ask_slot = 0;  // the next stage to request (see stream_bulk)
+    auto request = [&]() {
+        const int item = int(blockIdx.x) + ask_round * int(gridDim.x), segment = warp + ask_j * kBulkWarps;
+        const int slot = ask_slot;
+        if (++ask_j == per_item) { ask_j = 0; ++ask_round; }
+        if (++ask_slot == kStages) ask_slot = 0;
+        const uint32_t bar = bars + 8 * slot;
+        if (lane == 0) {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kStageBytes) : "memory");
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                             ring_address + slot * kStageBytes),
+                         "l"(&map_w), "r"(bar), "r"(segment * SEG), "r"(item * ROWS)
+                         : "memory");
+        }
+    };
+    // this lane's 16 digits of a 64-value piece start at 16 t of token g's plane; its outputs are tokens 2 t and 2 t + 1
+    const int8_t* plane0 = planes + int64_t(g) * 3 * k + 16 * t;
+    const float* my_scales = scales + 2 * t;
+
+    long long requested = 0;
+    for (; requested < total && requested < kStages; ++requested) request();
+    bool ok = true;
+    long long landed = 0;
+    int slot = 0;
+    uint32_t parity = 0;  // of the stage the warp consumes next
+    for (int round = 0; round < my_items; ++round) {
+        float acc[RB][4];
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb) acc[rb][0] = acc[rb][1] = acc[rb][2] = acc[rb][3] = 0.f;
+        for (int j = 0; j < per_item; ++j) {
+            const int segment = warp + j * kBulkWarps;
+            // digits and scales of the stage's runs: independent of the weights, requested before the wait
+            uint4 digits[RUNS][3][2];
+            float2 scale[RUNS];
+#pragma unroll
+            for (int run = 0; run < RUNS; ++run) {
+                const int k0 = segment * SEG + run * kPlaneRun;
+                const bool inside = k0 < k;
+                scale[run] = inside ? __ldg(reinterpret_cast<const float2*>(my_scales + (k0 / kPlaneRun) * kPlaneTokens)) : make_float2(0.f, 0.f);
+#pragma unroll
+                for (int p = 0; p < 3; ++p)
+#pragma unroll
+                    for (int piece = 0; piece < 2; ++piece)
+                        digits[run][p][piece] = inside ? __ldg(reinterpret_cast<const uint4*>(plane0 + int64_t(p) * k + k0 + piece * kStreamChunk))
+                                                       : make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (ok) ok = __all_sync(0xffffffffu, bulk_wait(bars + 8 * slot, parity, gave_up));
+            if (ok) {
+                ++landed;
+                const uint8_t* stage = ring + slot * kStageBytes;
+#pragma unroll
+                for (int run = 0; run < RUNS; ++run) {
+#pragma unroll
+                    for (int rb = 0; rb < RB; ++rb) {
+                        int sums[3][4];
+#pragma unroll
+                        for (int p = 0; p < 3; ++p) sums[p][0] = sums[p][1] = sums[p][2] = sums[p][3] = 0;
+#pragma unroll
+                        for (int piece = 0; piece < 2; ++piece) {
+                            const int offset = run * kPlaneRun + piece * kStreamChunk + 16 * t;
+                            const uint4 row0 = *reinterpret_cast<const uint4*>(stage + (rb * 16 + g) * SEG + offset);
+                            const uint4 row1 = kHalf ? make_uint4(0u, 0u, 0u, 0u) : *reinterpret_cast<const uint4*>(stage + (rb * 16 + g + 8) * SEG + offset);
+#pragma unroll
+                            for (int p = 0; p < 3; ++p) {
+                                const uint4 d = digits[run][p][piece];
+                                mma_s8_16x8x32(sums[p], row0.x, row1.x, row0.y, row1.y, d.x, d.y);
+                                mma_s8_16x8x32(sums[p], row0.z, row1.z, row0.w, row1.w, d.z, d.w);
+                            }
+                        }
+                        // exact INT32 sums of the run (below 2^21 in magnitude) -> FP32, planes combined, scaled by the token's power of two
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float combined = fmaf(float(sums[2][e]), 1.f / 16384.f, fmaf(float(sums[1][e]), 1.f / 128.f, float(sums[0][e])));
+                            acc[rb][e] = fmaf(combined, (e & 1) ? scale[run].y : scale[run].x, acc[rb][e]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (ok && requested < total) {
+                request();
+                ++requested;
+            }
+            if (++slot == kStages) { slot = 0; parity ^= 1u; }
+        }
+        const int set = round % kBulkPartials;
+        if (ok && round >= kBulkPartials)
+            ok = __all_sync(0xffffffffu, bulk_wait(sums_free + 8 * set, uint32_t(round / kBulkPartials - 1) & 1u, gave_up));
+        if (ok) {
+#pragma unroll
+            for (int rb = 0; rb < RB; ++rb) {
+                partial[set][warp][2 * t][rb * 16 + g] = acc[rb][0];
+                partial[set][warp][2 * t + 1][rb * 16 + g] = acc[rb][1];
+                if (!kHalf) {
+                    partial[set][warp][2 * t][rb * 16 + g + 8] = acc[rb][2];
+                    partial[set][warp][2 * t + 1][rb * 16 + g + 8] = acc[rb][3];
+                }
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(sums_ready + 8 * set) : "memory");
+        }
+    }
+    if (!ok) {
+        for (long long pending = landed; pending < requested; ++pending) {
+            const long long start = clock64();
+            while (!bulk_stage_ready(bars + 8 * int(pending % kStages), uint32_t(pending / kStages) & 1u) && clock64() - start < kBulkWaitLimit / 8) {
+            }
         }
     }
 }
@@ -521,12 +760,12 @@ static int launch_cores(const void* x, int64_t ldx, const int8_t* w, const float
 // item reads all of x from L2) and reduce less often; fewer rows balance the items over the SMs better.
 static int plan_bulk(int m, int n, int k, int sms) {
     if (sms <= 0) sms = 148;
+    if (m > 16) return 0;  // 17-32 tokens: four token blocks per lane do not fit the registers of a 17-warp CTA; stream_mma is faster there
     int best = 0;
     double best_score = 0.0;
     for (int rows = 8; rows <= 32; rows *= 2) {
         const int segment = rows >= 32 ? 128 : 256;
         if (k / segment < kBulkWarps) continue;  // fewer K segments than warps: warps would idle
-        if (rows == 32 && m > 16) continue;        // two sets of partial sums of 32 rows x 32 tokens x 16 warps do not fit beside the rings
         const int items = (n + rows - 1) / rows, rounds = (items + sms - 1) / sms;
         const double balance = double(items) / (double(sms) * rounds), activations = 1.0 + 0.3 * 2.0 * m / rows;
         const double score = balance / activations * (1.0 + 0.0005 * rows);  // ties go to the larger item
@@ -573,11 +812,45 @@ static int launch_bulk(const void* x, int64_t ldx, const int8_t* w, const float*
         case 208: WQ_BULK(2, 8);
         case 216: WQ_BULK(2, 16);
         case 232: WQ_BULK(2, 32);
-        case 408: WQ_BULK(4, 8);
-        case 416: WQ_BULK(4, 16);
     }
 #undef WQ_BULK
     return -2;
+}
+
+template <class T, int ROWS>
+static int launch_planes_shape(const int8_t* planes, const float* scales, const int8_t* w, const float* sw, const T* bias, const T* residual,
+                               const T* rscale, T* y, int m, int n, int k, int sms, cudaStream_t stream) {
+    using S = BulkShape<1, ROWS>;
+    auto kernel = stream_planes<T, ROWS>;
+    static bool configured[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device < 0 || device >= 64 || !configured[device]) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes);
+        if (e != cudaSuccess) return int(e);
+        if (device >= 0 && device < 64) configured[device] = true;
+    }
+    CUtensorMap map_w;
+    if (!make_byte_matrix_map(&map_w, w, n, k, S::kSegment, ROWS)) return int(cudaErrorNotSupported);
+    const int items = (n + ROWS - 1) / ROWS;
+    kernel<<<items < sms ? items : sms, kBulkThreads, S::kSmemBytes, stream>>>(map_w, planes, scales, sw, bias, residual, rscale, y, m, n, k);
+    return int(cudaGetLastError());
+}
+
+// The digit planes of the activations into `workspace`, then the INT8 tensor-core kernel.
+template <class T>
+static int launch_planes(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
+                         void* y, int m, int n, int k, int rows, int sms, void* workspace, cudaStream_t stream) {
+    int8_t* planes = static_cast<int8_t*>(workspace);
+    float* scales = reinterpret_cast<float*>(planes + int64_t(kPlaneTokens) * 3 * k);
+    const int units = (k / kPlaneRun) * kPlaneTokens;
+    split_planes<T><<<(units + 7) / 8, 256, 0, stream>>>(static_cast<const T*>(x), ldx, planes, scales, m, k);
+    auto b = static_cast<const T*>(bias), r = static_cast<const T*>(residual), rs = static_cast<const T*>(rscale);
+    auto out = static_cast<T*>(y);
+    if (sms <= 0) sms = 148;
+    if (rows == 8) return launch_planes_shape<T, 8>(planes, scales, w, sw, b, r, rs, out, m, n, k, sms, stream);
+    if (rows == 16) return launch_planes_shape<T, 16>(planes, scales, w, sw, b, r, rs, out, m, n, k, sms, stream);
+    return launch_planes_shape<T, 32>(planes, scales, w, sw, b, r, rs, out, m, n, k, sms, stream);
 }
 
 // Status of the streaming kernels on the current device: 0, or 1 when a wait for weight data gave up; clears it.
@@ -599,6 +872,29 @@ static int device_sms() {
 }  // namespace wq
 
 using namespace wq;
+
+// Bytes of workspace wq8_stream_planes needs for this shape, 0 when the shape is not one of its own (more than 8 tokens, K not a
+// multiple of 128, or too few K segments for the 16 warps).
+WQ_API int64_t wq8_stream_planes_workspace(int m, int n, int k, int sms) {
+    if (m <= 0 || m > kPlaneTokens || n <= 0 || k <= 0 || k % kPlaneRun || !plan_bulk(m, n, k, sms)) return 0;
+    return int64_t(kPlaneTokens) * 3 * k + int64_t(k / kPlaneRun) * kPlaneTokens * 4;
+}
+
+// Weight-only INT8 linear for at most 8 tokens with the activations split into INT8 digit planes (see stream_planes): the weights go into
+// INT8 tensor-core MMAs as they are.  workspace: wq8_stream_planes_workspace() bytes, 16-byte aligned.  Values: FP32 sums of exact
+// INT32 dot products per 128 values of K; an activation more than 2^14 times smaller than the largest of its 128 is truncated.
+WQ_API int wq8_stream_planes(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
+                             void* y, int m, int n, int k, int dtype, int sms, void* workspace, cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (dtype != 0 && dtype != 1) return -1;
+    if (m > kPlaneTokens || k <= 0 || k % kPlaneRun || ldx % 4 || (reinterpret_cast<uintptr_t>(x) & 7) || (reinterpret_cast<uintptr_t>(w) & 15) || !workspace ||
+        (reinterpret_cast<uintptr_t>(workspace) & 15))
+        return -2;
+    const int rows = plan_bulk(m, n, k, sms);
+    if (!rows) return -2;
+    if (dtype == 0) return launch_planes<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, workspace, stream);
+    return launch_planes<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, workspace, stream);
+}
 
 WQ_API void wq8_small_workspace(int m, int n, int k, int sms, int64_t* sizes) {
     const StreamPlan p = plan_stream(n, k, sms, true);

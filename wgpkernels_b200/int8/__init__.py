@@ -88,6 +88,9 @@ def load_library(path=None):
     lib.wq8_small_workspace.argtypes = [i, i, i, i, p]
     lib.wq8_small_workspace.restype = None
     lib.wq8_gemv_lines.argtypes = [p, i64, p, p, p, p, p, p, i, i, i, i, p]
+    lib.wq8_stream_planes_workspace.argtypes = [i, i, i, i]
+    lib.wq8_stream_planes_workspace.restype = i64
+    lib.wq8_stream_planes.argtypes = [p, i64, p, p, p, p, p, p, i, i, i, i, i, p, p]
     lib.wq8_l2_flush.argtypes = [i, i64, p]
     lib.wq8_l2_flush_release.restype = None
     lib.wq8_debug_block_sums.argtypes = [p, p, p, i, i, i, i, p]
@@ -415,6 +418,22 @@ def gemm(a, a_lo, sa, b, sb, bias, out_dtype, split=None, variant=None, out=None
     return y
 
 
+def _stream_planes(lib, x, weight, scale, bias, residual, residual_scale, y):
+    """At most 8 tokens: the activations split into INT8 digit planes (exact to 2^-14 of the largest of every 128 values), the weights on
+    INT8 tensor cores as they are.  False when the shape or the alignment is not this kernel's."""
+    m, k = x.shape
+    n, sms = weight.shape[0], _sm_count(x.device)
+    if m > 8 or x.stride(0) % 4 or x.data_ptr() % 8 or weight.data_ptr() % 16:
+        return False
+    size = lib.wq8_stream_planes_workspace(m, n, k, sms)
+    if not size:
+        return False
+    workspace = torch.empty(size, dtype=torch.uint8, device=x.device)
+    _check(lib.wq8_stream_planes(x.data_ptr(), x.stride(0), weight.data_ptr(), scale.data_ptr(), _ptr(bias), _ptr(residual), _ptr(residual_scale),
+                                 y.data_ptr(), m, n, k, _DTYPES[x.dtype], sms, workspace.data_ptr(), _stream(x.device)))
+    return True
+
+
 def small(x, weight, scale, bias=None, residual=None, residual_scale=None, out=None):
     """Weight-only INT8 for at most 32 tokens: unquantized activations, FP32 accumulation.  K multiple of 64."""
     lib = _require()
@@ -422,6 +441,8 @@ def small(x, weight, scale, bias=None, residual=None, residual_scale=None, out=N
     n = weight.shape[0]
     sms = _sm_count(x.device)
     y = torch.empty((m, n), dtype=x.dtype, device=x.device) if out is None else out
+    if _stream_planes(lib, x, weight, scale, bias, residual, residual_scale, y):
+        return y
     lib.wq8_small_workspace(m, n, k, sms, _sizes)
     slots = torch.empty(_sizes[0] // 4, dtype=torch.float32, device=x.device) if _sizes[0] else None
     stream = _stream(x.device)
@@ -436,6 +457,8 @@ def gemv_lines(x, weight, scale, bias=None, residual=None, residual_scale=None, 
     lib = _require()
     m, k = x.shape
     y = torch.empty((m, weight.shape[0]), dtype=x.dtype, device=x.device) if out is None else out
+    if _stream_planes(lib, x, weight, scale, bias, residual, residual_scale, y):
+        return y
     _check(lib.wq8_gemv_lines(x.data_ptr(), x.stride(0), weight.data_ptr(), scale.data_ptr(), _ptr(bias), _ptr(residual), _ptr(residual_scale),
                               y.data_ptr(), m, weight.shape[0], k, _DTYPES[x.dtype], _stream(x.device)))
     return y
