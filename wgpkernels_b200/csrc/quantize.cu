@@ -238,7 +238,9 @@ __global__ void __launch_bounds__(kRowThreads) transform_rows(const T* __restric
         inv_rms = inverse_rms(cta_sum_ordered(ss, slots), k, eps);
     }
     constexpr float norm = group_norm<GROUP>();
-    for (int base = warp * kChunk; base < k; base += 8 * kChunk) {
+    // gridDim.y CTAs share a row when no row statistic is needed: with one or a few rows every warp then has one chunk and one trip to
+    // memory instead of a chain of them
+    for (int base = (blockIdx.y * 8 + warp) * kChunk; base < k; base += gridDim.y * 8 * kChunk) {
         float v[8];
         const bool valid = base + lane * 8 < k;
         load_op<T, ACT>(src, k, base + lane * 8, v, valid);
@@ -378,11 +380,14 @@ static int launch_transform(const void* x, void* out, int m, int k, int64_t ldx,
     auto src = static_cast<const T*>(x);
     auto aw = static_cast<const T*>(act_weight);
     auto dst = static_cast<T*>(out);
+    // few rows: the CTAs of a row take its chunks in turn (not with rms_norm, whose row sum is formed inside one CTA)
+    const int chunk_groups = (k + 8 * kChunk - 1) / (8 * kChunk);
+    const dim3 grid(m, m < 64 ? (chunk_groups < 64 ? chunk_groups : 64) : 1);
     switch (act) {
-        case kActNone: transform_rows<T, GROUP, kActNone><<<m, kRowThreads, 0, stream>>>(src, dst, k, ldx, aw, eps); break;
+        case kActNone: transform_rows<T, GROUP, kActNone><<<grid, kRowThreads, 0, stream>>>(src, dst, k, ldx, aw, eps); break;
         case kActRms: transform_rows<T, GROUP, kActRms><<<m, kRowThreads, 0, stream>>>(src, dst, k, ldx, aw, eps); break;
-        case kActSwiglu: transform_rows<T, GROUP, kActSwiglu><<<m, kRowThreads, 0, stream>>>(src, dst, k, ldx, aw, eps); break;
-        case kActGelu: transform_rows<T, GROUP, kActGelu><<<m, kRowThreads, 0, stream>>>(src, dst, k, ldx, aw, eps); break;
+        case kActSwiglu: transform_rows<T, GROUP, kActSwiglu><<<grid, kRowThreads, 0, stream>>>(src, dst, k, ldx, aw, eps); break;
+        case kActGelu: transform_rows<T, GROUP, kActGelu><<<grid, kRowThreads, 0, stream>>>(src, dst, k, ldx, aw, eps); break;
         default: return -1;
     }
     return int(cudaGetLastError());

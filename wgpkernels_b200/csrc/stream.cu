@@ -756,21 +756,22 @@ static int launch_cores(const void* x, int64_t ldx, const int8_t* w, const float
     return int(cudaGetLastError());
 }
 
-// Rows per work item of stream_bulk (0: the shape is left to stream_mma).  More rows per item read the activations fewer times (every
-// item reads all of x from L2) and reduce less often; fewer rows balance the items over the SMs better.
+// Rows per work item of stream_bulk / stream_planes (0: the shape is left to stream_mma).  More rows per item read the activations fewer
+// times (every item reads all of x from L2), reduce less often and were the faster choice at every measured shape; fewer rows only when
+// the larger items would leave more than a fifth of the SMs' time idle.
 static int plan_bulk(int m, int n, int k, int sms) {
     if (sms <= 0) sms = 148;
     if (m > 16) return 0;  // 17-32 tokens: four token blocks per lane do not fit the registers of a 17-warp CTA; stream_mma is faster there
     int best = 0;
-    double best_score = 0.0;
-    for (int rows = 8; rows <= 32; rows *= 2) {
+    double best_balance = 0.0;
+    for (int rows = 32; rows >= 8; rows /= 2) {
         const int segment = rows >= 32 ? 128 : 256;
         if (k / segment < kBulkWarps) continue;  // fewer K segments than warps: warps would idle
         const int items = (n + rows - 1) / rows, rounds = (items + sms - 1) / sms;
-        const double balance = double(items) / (double(sms) * rounds), activations = 1.0 + 0.3 * 2.0 * m / rows;
-        const double score = balance / activations * (1.0 + 0.0005 * rows);  // ties go to the larger item
-        if (score > best_score) {
-            best_score = score;
+        const double balance = double(items) / (double(sms) * rounds);
+        if (balance >= 0.8) return rows;
+        if (balance > best_balance) {
+            best_balance = balance;
             best = rows;
         }
     }
