@@ -331,6 +331,13 @@ def main():
         peak, peak_source = 2 * peaks["bf16_tflops_sustained"], "2 x MEASURED_PEAKS bf16_tflops_sustained (INT8 MMA rate = 2 x BF16), of measured"
     else:
         peak, peak_source = 2 * 1400.0, "2 x 1.4 PFLOP/s sustained bf16, of fallback"
+    # DRAM bytes of one GEMM launch: the ncu capture of the same kernel at M = 4096 rows of c1 (dram__bytes_read + write = 275.2 MB,
+    # profiles/gemm_i8_tc_block_c1_rows4096.md) scaled by the rows: codes once, weights once per band of 2048 rows, outputs once.
+    traffic, traffic_source = None, None
+    if name == "c1" and world == 1:
+        traffic = 275.245e6 * m / 4096
+        traffic_source = "ncu capture at 4096 rows (275.2 MB) x rows / 4096"
+    local_m_bytes = m * k + 4 * m * ((k + 127) // 128) + (stop - start) * k + 4 * (stop - start) + 2 * m * (stop - start)
     launches_per_step = 2 + (1 if g.scale.dim() == 2 else 0)  # quantizer, GEMM, and the regrouping of group-scaled weight scales
     quant_bytes = m * k * (2 if c.act != "swiglu" else 4) + m * k + 4 * m * ((k + 127) // 128)
     line = {
@@ -344,7 +351,8 @@ def main():
                    "l2": "no flush: the operands of a step (x, q, W, y: > 1 GB) exceed the 126 MB L2"},
         "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
         "roofline": {"kernel": "gemm_i8_tc (block mode)", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
-                     "peak_source": peak_source, "nominal_dense_int8_tops": 4500.0, "traffic": None, "kernel_ms": gemm_ms,
+                     "peak_source": peak_source, "nominal_dense_int8_tops": 4500.0, "traffic": traffic, "traffic_source": traffic_source,
+                     "algorithmic_bytes": local_m_bytes, "kernel_ms": gemm_ms,
                      "quantizer": {"kernel_ms": quant_ms, "bound": "hbm", "achieved": quant_bytes / (quant_ms * 1e-3) / 1e9, "unit": "GB/s",
                                    "peak": peaks["hbm_gbs"] if peaks else 6650.0, "algorithmic_bytes": quant_bytes}},
         "device_status": status,
