@@ -229,6 +229,8 @@ struct GemmParams {
     const float* sb_blocks;  // group-scaled weights: the scales regrouped by block, (ceil(K/128), n_pad) with zeros past N
     int n_pad;               // row length of sb_blocks: N rounded up to 256
     int tma_y;      // the output maps describe the destinations: whole 32-column chunks leave through shared memory and the TMA unit
+    int wide_store;    // several destinations: the two staging tiles of a warp form one of 32 rows x 64 columns (128-byte rows cross NVLink
+                       // in half as many, twice as large writes); the output maps then have 64-column boxes and the 128-byte swizzle
     int destinations;  // copies of the output written by the TMA stores (1, or one per GPU of an N-sharded layer)
     int64_t ld_y, ld_residual;  // row strides in elements of y and of the residual
 };
@@ -531,7 +533,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             // y values of 32 columns starting at `col`: bias, residual, one rounding, store.  The accumulators of a tile live in registers,
             // so this body is instantiated once per 32 columns of the thread: it is kept short (the tile epilogue runs once per tile and
             // its instructions come from memory each time when the kernel outgrows the instruction cache).
-            auto emit = [&](const float* v, int col) {
+            auto emit = [&](const float* v, int col, int chunk) {
                 if (col >= p.n) return;
                 T* dst = y + int64_t(row) * p.ld_y + col;
                 const T* res = residual && row_ok ? residual + int64_t(row) * p.ld_residual + col : nullptr;
@@ -539,10 +541,14 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     // N is a multiple of 8 and every operand 16-byte aligned: eight outputs per step with 128-bit accesses; groups of eight
                     // are whole or absent at the right edge, rows past M are clipped by the TMA store (or skipped by the plain one)
                     const bool staged = p.tma_y != 0;
-                    const uint32_t stage_tile = my_stage + store_buffer * S::kStoreTile;
-                    if (staged) {
+                    const bool wide = S::kStoreBuffers == 2 && p.wide_store != 0, second = wide && (chunk & 1);
+                    const uint32_t stage_tile = wide ? my_stage : my_stage + store_buffer * S::kStoreTile;
+                    if (staged && !second) {
                         // the TMA store that last read this buffer must be done with it before the warp writes it again
-                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(S::kStoreBuffers - 1) : "memory");
+                        if (lane == 0) {
+                            if (wide) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                            else asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(S::kStoreBuffers - 1) : "memory");
+                        }
                         __syncwarp();
                     }
 #pragma unroll
@@ -575,25 +581,28 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                         packed.w = pack_pair<T>(out[6], out[7]);
                         if (staged) {
                             // row `lane` of the staging tile, 16-byte piece j / 8 at its place in the 64-byte swizzle
-                            const uint32_t piece = uint32_t(j >> 3) ^ ((uint32_t(lane) >> 1) & 3u);
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_tile + lane * 64 + piece * 16), "r"(packed.x),
+                            // (wide: piece 4 (chunk & 1) + j / 8 of a 128-byte row, 128-byte swizzle)
+                            const uint32_t piece = wide ? (uint32_t(((chunk & 1) << 2) | (j >> 3)) ^ (uint32_t(lane) & 7u))
+                                                        : (uint32_t(j >> 3) ^ ((uint32_t(lane) >> 1) & 3u));
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_tile + lane * (wide ? 128 : 64) + piece * 16), "r"(packed.x),
                                          "r"(packed.y), "r"(packed.z), "r"(packed.w)
                                          : "memory");
                         } else if (row_ok) {
                             *reinterpret_cast<uint4*>(dst + j) = packed;
                         }
                     }
-                    if (staged) {
+                    // wide: the store leaves with the pair's second chunk, or with the first when the second lies past N
+                    if (staged && (!wide || second || col + 32 >= p.n)) {
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         __syncwarp();
                         if (lane == 0) {
                             for (int d = 0; d < p.destinations; ++d)
                                 asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&out_maps.map[d]),
-                                             "r"(col), "r"(c.m0 + quarter * 32), "r"(stage_tile)
+                                             "r"(second ? col - 32 : col), "r"(c.m0 + quarter * 32), "r"(stage_tile)
                                              : "memory");
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
-                        if (++store_buffer == S::kStoreBuffers) store_buffer = 0;
+                        if (!wide && ++store_buffer == S::kStoreBuffers) store_buffer = 0;
                     }
                     return;
                 }
@@ -752,7 +761,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                 if constexpr (!DUMP) {
                     if (!(ok = await_params())) break;
 #pragma unroll
-                    for (int chunk = 0; chunk < kEpi / 32; ++chunk) emit(&accf[chunk * 32], col0 + chunk * 32);
+                    for (int chunk = 0; chunk < kEpi / 32; ++chunk) emit(&accf[chunk * 32], col0 + chunk * 32, chunk);
                     params_done();
                 }
 #ifdef WQ_TRACE
@@ -781,7 +790,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                         __syncwarp();
                         if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
                     }
-                    emit(v, col0 + chunk * 32);
+                    emit(v, col0 + chunk * 32, chunk);
                 }
                 params_done();
                 if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1u; }
@@ -893,15 +902,16 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int k, int bo
 }
 
 // (m, n) row-major matrix of 16-bit outputs -> tensor map with boxes of 32 rows x 32 columns, 64-byte swizzle (stores clip at the edges).
-static bool make_output_map(CUtensorMap* map, const void* base, int m, int n, int64_t ld, bool is_bf16) {
+// (wide: 32 rows x 64 columns, 128-byte swizzle)
+static bool make_output_map(CUtensorMap* map, const void* base, int m, int n, int64_t ld, bool is_bf16, bool wide) {
     EncodeTiled encode = encode_tiled();
     if (!encode) return false;
     const cuuint64_t dims[2] = {cuuint64_t(n), cuuint64_t(m)};
     const cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
-    const cuuint32_t box[2] = {32, 32};
+    const cuuint32_t box[2] = {wide ? 64u : 32u, 32};
     const cuuint32_t elem[2] = {1, 1};
     return encode(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                  elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  elem, CU_TENSOR_MAP_INTERLEAVE_NONE, wide ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -992,9 +1002,10 @@ static int launch(const GemmArgs& g, cudaStream_t stream) {
     for (int d = 1; d < p.destinations; ++d) bases |= reinterpret_cast<uintptr_t>(g.ys[d]);
     p.vector_io = g.n % 8 == 0 && p.ld_y % 8 == 0 && p.ld_residual % 8 == 0 && (bases & 15) == 0;
     p.tma_y = !DUMP && p.vector_io;
+    p.wide_store = S::kStoreBuffers == 2 && p.destinations > 1;
     for (int d = 0; d < kMaxDestinations; ++d) {
         if (p.tma_y && d < p.destinations)
-            p.tma_y = make_output_map(&out_maps.map[d], d == 0 ? p.y : g.ys[d], g.m, g.n, p.ld_y, std::is_same<T, bf16>::value);
+            p.tma_y = make_output_map(&out_maps.map[d], d == 0 ? p.y : g.ys[d], g.m, g.n, p.ld_y, std::is_same<T, bf16>::value, p.wide_store != 0);
         else
             out_maps.map[d] = map_a;
     }
