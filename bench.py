@@ -9,13 +9,16 @@ workload is the fused-QKV projection of a 14B video DiT on the 'block' path: M =
 bf16 output.  Metric: effective INT8 TOPS = 2 M N K / time, whole job.
 
   value      inputs resident in HBM; CUDA events around exactly K steps after W warm-up steps; max over ranks
-  e2e        the same call with HOST buffers: pinned x -> device, linear, y -> pinned host, copies inside the timed region
+  e2e        the same linear with HOST buffers through the package's call for them (wgpkernels_b200.host.HostLinear: pinned x -> device,
+             linear, y -> pinned host, pipelined over 4096-row chunks on three streams), copies inside the timed region
   roofline   the GEMM kernel alone (events around its launches): achieved TOPS against the tensor-core peak
   cpu_baseline  the FP32 dequantize-and-matmul statement of the linear (the reference's own CPU path, restated) on the host cores,
              on a bounded band of rows of the same workload
 
 With N > 1 the output channels are sharded over the ranks (each keeps N / g rows of the weight), every rank quantizes the replicated
-activation and the (M, N / g) slices are all-gathered over NCCL: total work is fixed ("strong" scaling).
+activation and its GEMM writes its (M, N / g) output columns into the full-width buffers of all ranks (--gather fused, TMA stores over
+NVLink from the tile epilogue) or the slices are all-gathered over NCCL afterwards (--gather nccl): total work is fixed ("strong"
+scaling).  Only the JSON line goes to stdout; tuner messages go to stderr.
 
 --impl reference times the CPU statement of the linear only (rank 0; the other ranks exit).
 """
@@ -119,7 +122,7 @@ def run_reference(args, rank):
             "config": {"workload": f"{args.workload}: {DESCRIPTIONS[args.workload]}", "sample": sample},
             "cpu_baseline": {"value": tops, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": tops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=RESULT_STREAM, flush=True)
 
 
 def run_few_tokens(args, rank):
@@ -191,10 +194,14 @@ def run_few_tokens(args, rank):
                          "algorithmic_bytes": moved, "peak_source": "MEASURED_PEAKS hbm_gbs, of measured" if peaks else "of fallback",
                          "plain_read": {"ms": probe_ms, "gbs": c.n * c.k / (probe_ms * 1e-3) / 1e9, "frac_of_it": probe_ms / ms * moved / (c.n * c.k),
                                         "what": "a plain read kernel over the weight's byte count, cold, same events"}}}
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=RESULT_STREAM, flush=True)
+
+
+RESULT_STREAM = sys.stdout  # the one JSON line goes here; everything else the process prints (tuner messages) goes to stderr
 
 
 def main():
+    sys.stdout = sys.stderr
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=20)
@@ -305,16 +312,27 @@ def main():
         host_y = torch.empty((m, n_total if world > 1 else g.weight.shape[0]), dtype=c.x.dtype).pin_memory()
         device_x = torch.empty_like(g.x)
 
-        def e2e_step():
-            device_x.copy_(host_x, non_blocking=True)
-            host_y.copy_(step(device_x), non_blocking=True)
+        if world == 1:
+            # the package's call for host-resident activations: copy in, linear and copy out pipelined over chunks of 4096 rows
+            from wgpkernels_b200.host import HostLinear
+            host_linear = HostLinear(g.weight, g.scale, g.bias, chunk_rows=4096)
+
+            def e2e_step():
+                host_linear(host_x, host_y, residual=g.residual, residual_scale=g.residual_scale, mode="block", act=c.act,
+                            act_weight=g.act_weight, eps=c.eps)
+        else:
+            def e2e_step():
+                device_x.copy_(host_x, non_blocking=True)
+                host_y.copy_(step(device_x), non_blocking=True)
 
         for _ in range(2):
             e2e_step()
         e2e_steps = max(3, min(args.steps, 10))
         e2e_ms = timed(e2e_step, e2e_steps)
         e2e = {"value": ops * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": host_x.numel() * host_x.element_size(),
-               "d2h_bytes_per_step": host_y.numel() * host_y.element_size(), "ms_per_step": e2e_ms / e2e_steps}
+               "d2h_bytes_per_step": host_y.numel() * host_y.element_size(), "ms_per_step": e2e_ms / e2e_steps,
+               "call": "wgpkernels_b200.host.HostLinear (pinned host x -> pinned host y, 4096-row chunks pipelined on three streams)" if world == 1
+               else "pinned host x -> device, ShardedLinear, device -> pinned host y"}
     clocks = sampler.stop() if sampler else None
 
     if rank != 0:
@@ -368,7 +386,7 @@ def main():
         tops, seconds, _ = cpu_reference_tops(name, rows, 3)
         line["cpu_baseline"] = {"value": tops, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "seconds": seconds,
                                 "sample": f"first {rows} rows of the workload, full K and N; FP32 dequantize + matmul (PyTorch CPU), median of 3"}
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=RESULT_STREAM, flush=True)
     if world > 1:
         dist.destroy_process_group()
 

@@ -1,0 +1,71 @@
+"""The INT8 linear for activations that live in host memory: copy in, compute and copy out run as a pipeline over row chunks.
+
+The reference has no counterpart (its callers hold the activations on the GPU).  A caller whose activations arrive from the host - an
+offloading pipeline, a data loader, another process - pays two PCIe transfers per call; done one after the other around the linear they
+cost several times the linear itself.  Here three streams work on different row chunks at the same time: chunk i + 1 is copied to the
+device while chunk i is multiplied and chunk i - 1 travels back (PCIe is full duplex), with two device buffers on each side.
+"""
+import torch
+
+from . import int8
+
+
+class HostLinear:
+    """y_host[rows] = linear(x_host[rows]) for pinned host tensors, pipelined over chunks of `chunk_rows` rows.  The device buffers and
+    streams are kept between calls.  kwargs: those of `int8.linear` (mode, act, act_weight, eps, group, precise, residual_scale);
+    a device `residual` (M, N) is read per chunk."""
+
+    def __init__(self, weight, scale, bias=None, chunk_rows=4096, device=None):
+        self.weight, self.scale, self.bias = weight, scale, bias
+        self.chunk_rows = chunk_rows
+        self.device = weight.device if device is None else device
+        self.copy_in = torch.cuda.Stream(self.device)
+        self.copy_out = torch.cuda.Stream(self.device)
+        self._buffers = {}
+
+    def _chunk_buffers(self, k, n, dtype):
+        key = (k, n, dtype)
+        if key not in self._buffers:
+            self._buffers[key] = ([torch.empty((self.chunk_rows, k), dtype=dtype, device=self.device) for _ in range(2)],
+                                  [torch.empty((self.chunk_rows, n), dtype=dtype, device=self.device) for _ in range(2)])
+        return self._buffers[key]
+
+    def __call__(self, x_host, out_host, residual=None, **kwargs):
+        if not (x_host.is_pinned() and out_host.is_pinned()):
+            raise ValueError("x_host and out_host must be pinned host tensors (asynchronous copies)")
+        m, k = x_host.shape
+        n = self.weight.shape[0]
+        if tuple(out_host.shape) != (m, n) or out_host.dtype != x_host.dtype:
+            raise ValueError("out_host must be (M, N) of x's dtype")
+        xs, ys = self._chunk_buffers(k, n, x_host.dtype)
+        compute = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(compute)
+        self.copy_in.wait_event(start)   # the buffers may still be read by work queued before this call
+        self.copy_out.wait_event(start)
+        computed, stored = [None, None], [None, None]  # per buffer: the event after its last multiply / its last copy out
+        for index, first in enumerate(range(0, m, self.chunk_rows)):
+            rows = min(self.chunk_rows, m - first)
+            slot = index % 2
+            with torch.cuda.stream(self.copy_in):
+                if computed[slot] is not None:
+                    self.copy_in.wait_event(computed[slot])  # the multiply that read this input buffer two chunks ago
+                xs[slot][:rows].copy_(x_host[first:first + rows], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(self.copy_in)
+            compute.wait_event(arrived)
+            if stored[slot] is not None:
+                compute.wait_event(stored[slot])  # the copy out that read this output buffer two chunks ago
+            int8.linear(xs[slot][:rows], self.weight, self.scale, self.bias, out=ys[slot][:rows],
+                        residual=None if residual is None else residual[first:first + rows], **kwargs)
+            computed[slot] = torch.cuda.Event()
+            computed[slot].record(compute)
+            with torch.cuda.stream(self.copy_out):
+                self.copy_out.wait_event(computed[slot])
+                out_host[first:first + rows].copy_(ys[slot][:rows], non_blocking=True)
+                stored[slot] = torch.cuda.Event()
+                stored[slot].record(self.copy_out)
+        for event in stored:
+            if event is not None:
+                compute.wait_event(event)  # the caller's stream sees the call as complete once every chunk is back on the host
+        return out_host
