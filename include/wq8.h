@@ -77,7 +77,8 @@ void wq8_gemm_workspace(int m, int n, int k, int variant, int sms, int split, in
 int wq8_gemm_select(int m, int n, int k, int hilo, int sms);
 
 /* wq8_gemm of `count` (1 to 4) weights bs[s] (rows, K) of one input in one launch, outputs ys[s] (M, rows),
- * rows a multiple of 8; per-channel weight scales only; no residual.  Replaces int8_gemm.cu:1663-1676. */
+ * rows a multiple of 8; per-channel weight scales only; no residual.  Here: one launch per weight (same values).  -4 for bad
+ * segments (count, rows, NULL entries, group-scaled variants).  Replaces int8_gemm.cu:1663-1676. */
 int wq8_gemm_segments(const int8_t* a, const int8_t* a_lo, const float* sa, const int8_t* const* bs, const float* const* sbs,
                       const void* const* biases, void* const* ys, int count, int rows, int m, int k, int dtype, int variant, int sms,
                       int split, int* workspace, int* counters, wq8_stream_t stream);

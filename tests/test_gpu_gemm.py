@@ -187,3 +187,26 @@ def test_column_ranges_and_several_outputs(wq, mode, residual):
     wq.gemm(dev(a), dev(a_lo), dev(sa), dev(b[:515]), dev(sb[:515]), dev(bias[:515]), dtype, 0, MODES[mode], out=odd[:, 3:518])
     assert torch.equal(odd[:, 3:518], expected_odd) and bool((odd[:, :3] == 7.0).all()) and bool((odd[:, 518:] == 7.0).all())
     assert wq.debug_status() == 0
+
+
+def test_segments_entry_point(wq):
+    """wq8_gemm_segments of the C ABI: three weights of one quantized input, each output equal to wq8_gemm's on that weight."""
+    import ctypes
+    m, rows, k, dtype = 300, 264, 640, torch.bfloat16
+    base, a, _, sa, b, sb, bias, _, _ = operands("block", m, 3 * rows, k, dtype, 91)
+    ga, gsa, gb, gsb, gbias = a.cuda(), sa.cuda(), b.cuda(), sb.cuda(), bias.cuda()
+    weights = [gb[s * rows:(s + 1) * rows] for s in range(3)]
+    scales = [gsb[s * rows:(s + 1) * rows].contiguous() for s in range(3)]
+    biases = [gbias[:rows].contiguous(), None, gbias[rows:2 * rows].contiguous()]
+    outputs = [torch.empty((m, rows), dtype=dtype, device="cuda") for _ in range(3)]
+    lib = wq._require()
+    p, i = ctypes.c_void_p, ctypes.c_int
+    lib.wq8_gemm_segments.argtypes = [p, p, p, p, p, p, p, i, i, i, i, i, i, i, i, p, p, p]
+    pointers = lambda tensors: (ctypes.c_void_p * 4)(*[None if t is None else t.data_ptr() for t in tensors])
+    code = lib.wq8_gemm_segments(ga.data_ptr(), None, gsa.data_ptr(), pointers(weights), pointers(scales), pointers(biases), pointers(outputs), 3, rows,
+                                 m, k, 1, 10, 148, 0, None, None, wq._stream(ga.device))
+    assert code == 0
+    for weight, scale, bias_s, out in zip(weights, scales, biases, outputs):
+        assert torch.equal(out, wq.gemm(ga, None, gsa, weight, scale, bias_s, dtype, 0, 10))
+    assert lib.wq8_gemm_segments(ga.data_ptr(), None, gsa.data_ptr(), pointers(weights), pointers(scales), pointers(biases), pointers(outputs), 5, rows,
+                                 m, k, 1, 10, 148, 0, None, None, wq._stream(ga.device)) == -4

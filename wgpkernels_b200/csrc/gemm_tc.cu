@@ -1077,9 +1077,21 @@ WQ_API void wq8_gemm_workspace(int, int n, int k, int variant, int, int, int64_t
 
 WQ_API int wq8_gemm_select(int, int, int, int hilo, int) { return hilo ? 1 : 0; }
 
-WQ_API int wq8_gemm_segments(const int8_t*, const int8_t*, const float*, const int8_t* const*, const float* const*, const void* const*, void* const*,
-                             int, int, int, int, int, int, int, int, int*, int*, cudaStream_t) {
-    return -4;
+// One launch per weight: the quantized input stays in L2 between them (a band of 2048 rows of codes is 10 MB), the values are those of
+// wq8_gemm on each weight.  Per-channel weight scales only, as in the reference.
+WQ_API int wq8_gemm_segments(const int8_t* a, const int8_t* a_lo, const float* sa, const int8_t* const* bs, const float* const* sbs,
+                             const void* const* biases, void* const* ys, int count, int rows, int m, int k, int dtype, int variant, int sms, int split,
+                             int* workspace, int* counters, cudaStream_t stream) {
+    if (count < 1 || count > 4 || rows <= 0 || rows % 8 || !bs || !sbs || !ys) return -4;
+    if (variant >= 12 && variant <= 14) return -4;
+    for (int s = 0; s < count; ++s)
+        if (!bs[s] || !sbs[s] || !ys[s]) return -4;
+    for (int s = 0; s < count; ++s) {
+        const int code = wq8_gemm(a, a_lo, sa, bs[s], sbs[s], biases ? biases[s] : nullptr, nullptr, nullptr, ys[s], m, rows, k, dtype, variant, sms, split,
+                                  workspace, counters, stream);
+        if (code) return code;
+    }
+    return 0;
 }
 
 WQ_API int wq8_debug_block_sums(const int8_t* a, const int8_t* b, int32_t* sums, int m, int n, int k, int sms, cudaStream_t stream) {

@@ -590,8 +590,8 @@ __global__ void __launch_bounds__(kBulkThreads, 1) stream_planes(const __grid_co
 #pragma unroll
             for (int run = 0; run < RUNS; ++run) {
                 const int k0 = segment * SEG + run * kPlaneRun;
-                const bool inside = k0 < k;
-                scale[run] = inside ? __ldg(reinterpret_cast<const float2*>(my_scales + (k0 / kPlaneRun) * kPlaneTokens)) : make_float2(0.f, 0.f);
+                const bool inside = k0 < k && g < m;  // token slots past M hold zeros: not fetched (their MMA columns are never stored)
+                scale[run] = k0 < k ? __ldg(reinterpret_cast<const float2*>(my_scales + (k0 / kPlaneRun) * kPlaneTokens)) : make_float2(0.f, 0.f);
 #pragma unroll
                 for (int p = 0; p < 3; ++p)
 #pragma unroll
