@@ -97,3 +97,36 @@ def test_workspace_queries(lib):
     # many channels: every SM streams without splitting
     lib.wq8_small_workspace(16, 28672, 4096, 148, sizes)
     assert sizes[0] == 0 and sizes[1] == 0
+
+
+def test_additions_check_their_arguments(lib):
+    """The entry points this library adds: argument checks that come before any CUDA call, and the workspace sizes."""
+    i, i64, p = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p
+    lib.wq8_gemm_multi.argtypes = [p, p, p, p, p, p, p, i64, p, p, i, i64, i, i, i, i, i, i, p, p]
+    lib.wq8_stream_planes_workspace.argtypes = [i, i, i, i]
+    lib.wq8_stream_planes_workspace.restype = i64
+    lib.wq8_stream_planes.argtypes = [p, i64, p, p, p, p, p, p, i, i, i, i, i, p, p]
+    lib.wq8_gemm_segments.argtypes = [p, p, p, p, p, p, p, i, i, i, i, i, i, i, i, p, p, p]
+    one = ctypes.c_void_p(16)
+    targets = (ctypes.c_void_p * 8)(*([16] * 8))
+    assert lib.wq8_gemm_multi(one, None, one, one, one, None, None, 0, None, targets, 0, 96, 8, 96, 256, 1, 10, 148, None, None) == -2   # no destination
+    assert lib.wq8_gemm_multi(one, None, one, one, one, None, None, 0, None, targets, 9, 96, 8, 96, 256, 1, 10, 148, None, None) == -2   # too many
+    assert lib.wq8_gemm_multi(one, None, one, one, one, None, None, 0, None, targets, 2, 64, 8, 96, 256, 1, 10, 148, None, None) == -2   # row stride < N
+    assert lib.wq8_gemm_multi(one, None, one, one, one, None, None, 0, None, None, 1, 96, 8, 96, 256, 1, 10, 148, None, None) == -2
+    assert lib.wq8_gemm_multi(None, None, None, None, None, None, None, 0, None, None, 0, 0, 0, 96, 256, 1, 10, 148, None, None) == 0    # empty
+    assert lib.wq8_stream_planes_workspace(4, 4096, 4096, 148) == 8 * 3 * 4096 + (4096 // 128) * 8 * 4
+    assert lib.wq8_stream_planes_workspace(9, 4096, 4096, 148) == 0      # more than 8 tokens
+    assert lib.wq8_stream_planes_workspace(4, 4096, 4096 + 64, 148) == 0  # K not a multiple of 128
+    assert lib.wq8_stream_planes_workspace(4, 4096, 512, 148) == 0        # too few K segments
+    assert lib.wq8_stream_planes(one, 4096, one, one, None, None, None, one, 9, 4096, 4096, 1, 148, one, None) == -2
+    assert lib.wq8_stream_planes(one, 4096, one, one, None, None, None, one, 4, 4096, 4096, 1, 148, None, None) == -2  # no workspace
+    assert lib.wq8_stream_planes(one, 4096, one, one, None, None, None, one, 4, 4096, 4096, 2, 148, one, None) == -1
+    four = (ctypes.c_void_p * 4)(16, 16, 16, 16)
+    assert lib.wq8_gemm_segments(one, None, one, four, four, four, four, 5, 96, 8, 256, 1, 10, 148, 0, None, None, None) == -4
+    assert lib.wq8_gemm_segments(one, None, one, four, four, four, four, 2, 100, 8, 256, 1, 10, 148, 0, None, None, None) == -4  # rows % 8
+    assert lib.wq8_gemm_segments(one, None, one, four, four, four, four, 2, 96, 8, 256, 1, 12, 148, 0, None, None, None) == -4   # group scales
+    sizes = (ctypes.c_int64 * 2)()
+    lib.wq8_gemm_workspace(8, 300, 640, 12, 148, 0, sizes)
+    assert sizes[0] == 5 * 512 * 4 and sizes[1] == 0
+    lib.wq8_gemm_workspace(8, 300, 640, 10, 148, 1, sizes)
+    assert sizes[0] == 0 and sizes[1] == 0

@@ -290,14 +290,6 @@ static int persistent_ctas(int64_t warps_of_work) {
     return int(ctas < cap ? (ctas < 1 ? 1 : ctas) : cap);
 }
 
-// CTAs of the persistent one-row-at-a-time kernels: every row its own CTA up to eight resident CTAs per SM.
-static int row_ctas(int m) {
-    int device = 0, sms = 148;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    return m < sms * 8 ? m : sms * 8;
-}
-
 template <class T, int GROUP, int ACT>
 static int launch_blocks(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, const void* act_weight, float eps, cudaStream_t stream) {
     auto src = static_cast<const T*>(x);
