@@ -64,41 +64,56 @@ def _require():
     return _lib
 
 
+# ctypes signatures of the C ABI (include/wq8.h): v = pointer, i = int, l = int64, f = float; the part after "->" is the result
+# ("" = void, default int).
+_SIGNATURES = {
+    "wq8_quantize": "vvvviiliiivfv",
+    "wq8_quantize_blocks": "vvviiliiivfvv",
+    "wq8_transform_rows": "vviiliiivfv",
+    "wq8_rotate_groups": "vviiliiv",
+    "wq8_gemm": "vvvvvvvvviiiiiiivvv",
+    "wq8_gemm_multi": "vvvvvvvlvviliiiiiivv",
+    "wq8_gemm_workspace": "iiiiiiv->",
+    "wq8_gemm_select": "iiiii",
+    "wq8_small": "vlvvvvvviiiiivvv",
+    "wq8_small_workspace": "iiiiv->",
+    "wq8_gemv_lines": "vlvvvvvviiiiv",
+    "wq8_stream_planes_workspace": "iiii->l",
+    "wq8_stream_planes": "vlvvvvvviiiiivv",
+    "wq8_l2_flush": "ilv",
+    "wq8_l2_flush_release": "->",
+    "wq8_debug_block_sums": "vvviiiiv",
+    "wq8_debug_status": "",
+}
+_CTYPES = {"v": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_int64, "f": ctypes.c_float}
+
+
+def _bind(handle):
+    for name, signature in _SIGNATURES.items():
+        arguments, arrow, result = signature.partition("->")
+        function = getattr(handle, name)
+        function.argtypes = [_CTYPES[letter] for letter in arguments]
+        function.restype = (_CTYPES[result] if result else None) if arrow else ctypes.c_int
+
+
 def load_library(path=None):
-    """Loads libwgp_int8.so (raises when it is missing or has another ABI) and allocates the per-device split-K counters."""
+    """Opens libwgp_int8.so and binds its entry points; RuntimeError when the file is missing or speaks another ABI.  Also creates the
+    zeroed counter buffer of every visible GPU."""
     global _lib, _weight_groups
-    location = Path(path or default_library_path()).resolve()
-    if not location.exists():
+    location = Path(default_library_path() if path is None else path).resolve()
+    if not location.is_file():
         raise RuntimeError(f"INT8 library not found at {location}; build it with `python -m wgpkernels_b200.build`")
-    lib = ctypes.CDLL(str(location))
-    if lib.wq8_abi() != ABI:
-        raise RuntimeError("INT8 GEMM library ABI mismatch; rebuild it")
-    _weight_groups = bool(lib.wq8_features() & 1)
-    p, i, i64, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
-    lib.wq8_quantize.argtypes = [p, p, p, p, i, i, i64, i, i, i, p, f, p]
-    lib.wq8_quantize_blocks.argtypes = [p, p, p, i, i, i64, i, i, i, p, f, p, p]
-    lib.wq8_transform_rows.argtypes = [p, p, i, i, i64, i, i, i, p, f, p]
-    lib.wq8_rotate_groups.argtypes = [p, p, i, i, i64, i, i, p]
-    lib.wq8_gemm.argtypes = [p, p, p, p, p, p, p, p, p, i, i, i, i, i, i, i, p, p, p]
-    lib.wq8_gemm_workspace.argtypes = [i, i, i, i, i, i, p]
-    lib.wq8_gemm_workspace.restype = None
-    lib.wq8_gemm_multi.argtypes = [p, p, p, p, p, p, p, i64, p, p, i, i64, i, i, i, i, i, i, p, p]
-    lib.wq8_gemm_select.argtypes = [i, i, i, i, i]
-    lib.wq8_small.argtypes = [p, i64, p, p, p, p, p, p, i, i, i, i, i, p, p, p]
-    lib.wq8_small_workspace.argtypes = [i, i, i, i, p]
-    lib.wq8_small_workspace.restype = None
-    lib.wq8_gemv_lines.argtypes = [p, i64, p, p, p, p, p, p, i, i, i, i, p]
-    lib.wq8_stream_planes_workspace.argtypes = [i, i, i, i]
-    lib.wq8_stream_planes_workspace.restype = i64
-    lib.wq8_stream_planes.argtypes = [p, i64, p, p, p, p, p, p, i, i, i, i, i, p, p]
-    lib.wq8_l2_flush.argtypes = [i, i64, p]
-    lib.wq8_l2_flush_release.restype = None
-    lib.wq8_debug_block_sums.argtypes = [p, p, p, i, i, i, i, p]
-    if torch.cuda.is_available():
-        for index in range(torch.cuda.device_count()):
-            _counters.setdefault(index, torch.zeros(_COUNTERS, dtype=torch.int32, device=torch.device("cuda", index)))
-    _lib = lib
-    return lib
+    handle = ctypes.CDLL(str(location))
+    found = handle.wq8_abi()
+    if found != ABI:
+        raise RuntimeError(f"INT8 GEMM library ABI mismatch ({found}, this module speaks {ABI}); rebuild it")
+    _bind(handle)
+    _weight_groups = handle.wq8_features() & 1 == 1
+    for index in range(torch.cuda.device_count() if torch.cuda.is_available() else 0):
+        if index not in _counters:
+            _counters[index] = torch.zeros(_COUNTERS, dtype=torch.int32, device=f"cuda:{index}")
+    _lib = handle
+    return handle
 
 
 def _check(code):
@@ -156,48 +171,52 @@ def _check_input(x, act):
 # ---------------------------------------------------------------------------------------------------------------------
 # activation preparation
 # ---------------------------------------------------------------------------------------------------------------------
+def _row_kernel(entry, x, group, act, act_weight, eps, outputs, scratch=()):
+    """One launch of a row-wise preparation kernel of the C ABI: the output pointers first (None for an absent one), then the common
+    tail (M, K, row stride, dtype, group, input operation, its weight, eps), `scratch` pointers and the stream."""
+    _check_input(x, act)
+    pointers = [None if t is None else t.data_ptr() for t in outputs]
+    tail = (x.shape[0], _width(x, act), x.stride(0), _DTYPES[x.dtype], group, ACTS[act], _ptr(act_weight), eps)
+    _check(getattr(_require(), entry)(x.data_ptr(), *pointers, *tail, *scratch, _stream(x.device)))
+
+
+def _like(x, act, dtype, *shape):
+    return torch.empty(shape or (x.shape[0], _width(x, act)), dtype=dtype, device=x.device)
+
+
 def quantize_blocks(x, group=0, act=None, act_weight=None, eps=0.0):
     """INT8 of op(x) with one FP32 scale per row and 128-element block of K: (q (M, K), scales (M, ceil(K / 128)))."""
-    lib = _require()
     _check_input(x, act)
-    m, k = x.shape[0], _width(x, act)
-    q = torch.empty((m, k), dtype=torch.int8, device=x.device)
-    scale = torch.empty((m, (k + 127) // 128), dtype=torch.float32, device=x.device)
-    _check(lib.wq8_quantize_blocks(x.data_ptr(), q.data_ptr(), scale.data_ptr(), m, k, x.stride(0), _DTYPES[x.dtype], group, ACTS[act],
-                                   _ptr(act_weight), eps, None, _stream(x.device)))
-    return q, scale
+    codes = _like(x, act, torch.int8)
+    scales = _like(x, act, torch.float32, x.shape[0], -(-_width(x, act) // 128))
+    _row_kernel("wq8_quantize_blocks", x, group, act, act_weight, eps, (codes, scales), scratch=(None,))
+    return codes, scales
 
 
 def quantize(x, group=0, hilo=False, act=None, act_weight=None, eps=0.0):
     """Row-wise INT8 of op(x): (hi, lo or None, FP32 row scales); with hilo, op(x) ~= scale * (hi + lo / 254)."""
-    lib = _require()
     _check_input(x, act)
-    m, k = x.shape[0], _width(x, act)
-    hi = torch.empty((m, k), dtype=torch.int8, device=x.device)
-    lo = torch.empty_like(hi) if hilo else None
-    scale = torch.empty(m, dtype=torch.float32, device=x.device)
-    _check(lib.wq8_quantize(x.data_ptr(), hi.data_ptr(), _ptr(lo), scale.data_ptr(), m, k, x.stride(0), _DTYPES[x.dtype], group, ACTS[act],
-                            _ptr(act_weight), eps, _stream(x.device)))
-    return hi, lo, scale
+    hi = _like(x, act, torch.int8)
+    lo = _like(x, act, torch.int8) if hilo else None
+    scales = _like(x, act, torch.float32, x.shape[0])
+    _row_kernel("wq8_quantize", x, group, act, act_weight, eps, (hi, lo, scales))
+    return hi, lo, scales
 
 
 def transform_rows(x, group=0, act=None, act_weight=None, eps=0.0):
     """op(x), rotated, rounded once to x's dtype: the unquantized activation of the few-token paths."""
-    lib = _require()
     _check_input(x, act)
-    m, k = x.shape[0], _width(x, act)
-    out = torch.empty((m, k), dtype=x.dtype, device=x.device)
-    _check(lib.wq8_transform_rows(x.data_ptr(), out.data_ptr(), m, k, x.stride(0), _DTYPES[x.dtype], group, ACTS[act], _ptr(act_weight), eps,
-                                  _stream(x.device)))
-    return out
+    ready = _like(x, act, x.dtype)
+    _row_kernel("wq8_transform_rows", x, group, act, act_weight, eps, (ready,))
+    return ready
 
 
 def rotate_groups(x, group):
     """ConvRot rotation in groups of 16, 64 or 256, rounded once to the input dtype."""
-    lib = _require()
-    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
-    _check(lib.wq8_rotate_groups(x.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1], x.stride(0), _DTYPES[x.dtype], group, _stream(x.device)))
-    return out
+    rotated = torch.empty_like(x, memory_format=torch.contiguous_format)
+    m, k = x.shape
+    _check(_require().wq8_rotate_groups(x.data_ptr(), rotated.data_ptr(), m, k, x.stride(0), _DTYPES[x.dtype], group, _stream(x.device)))
+    return rotated
 
 
 class Prepared:
@@ -215,16 +234,19 @@ class Prepared:
 
 def prepare(x, group=0, path="block", act=None, act_weight=None, eps=0.0):
     """op(x) prepared once for `path`; x: 2-D BF16 / FP16, rows 16-byte aligned; act_weight in x's dtype."""
-    if path in ("lines", "small"):
-        ready = transform_rows(x, group, act, act_weight, eps) if act else rotate_groups(x, group) if group else x
-        return Prepared(path, ready, None, None, x.dtype)
     if path == "block":
-        q, scale = quantize_blocks(x, group, act, act_weight, eps)
-        return Prepared(path, q, None, scale, x.dtype)
-    if path not in ("exact", "row"):
+        codes, scales = quantize_blocks(x, group, act, act_weight, eps)
+        return Prepared(path, codes, None, scales, x.dtype)
+    if path in ("exact", "row"):
+        hi, lo, scales = quantize(x, group, path == "exact", act, act_weight, eps)
+        return Prepared(path, hi, lo, scales, x.dtype)
+    if path not in ("lines", "small"):
         raise ValueError(f"unknown path {path!r}")
-    hi, lo, scale = quantize(x, group, path == "exact", act, act_weight, eps)
-    return Prepared(path, hi, lo, scale, x.dtype)
+    if act:
+        rows = transform_rows(x, group, act, act_weight, eps)
+    else:
+        rows = rotate_groups(x, group) if group else x
+    return Prepared(path, rows, None, None, x.dtype)
 
 
 # ---------------------------------------------------------------------------------------------------------------------
@@ -255,23 +277,33 @@ def _path_bucket(m):
     return m if m <= 16 else -(-m // 8) * 8 if m <= 128 else _rows_bucket(m)
 
 
+def _read_tuning_file():
+    """The configs of the tuning file, {} when it is absent, unreadable or written by another version of the kernels."""
+    try:
+        stored = json.loads(_TUNING_PATH.read_text(encoding="utf-8"))
+    except (OSError, ValueError):
+        return {}
+    if not isinstance(stored, dict) or stored.get("version") != _TUNING_VERSION or not isinstance(stored.get("configs"), dict):
+        return {}
+    return stored["configs"]
+
+
 def _cache():
+    """Tuned choices of this process, seeded once from the tuning file."""
     global _tuned
     if _tuned is None:
-        try:
-            payload = json.loads(_TUNING_PATH.read_text(encoding="utf-8"))
-            _tuned = payload["configs"] if payload.get("version") == _TUNING_VERSION else {}
-        except (OSError, ValueError, KeyError, AttributeError):
-            _tuned = {}
+        _tuned = _read_tuning_file()
     return _tuned
 
 
 def _save_cache():
+    """Writes the tuned choices next to the old file and swaps them in (several ranks may do so at once); failures are reported only."""
+    document = json.dumps({"version": _TUNING_VERSION, "configs": _tuned}, indent=1)
+    scratch = _TUNING_PATH.with_suffix(f".{os.getpid()}.tmp")
     try:
         _TUNING_PATH.parent.mkdir(parents=True, exist_ok=True)
-        temporary = _TUNING_PATH.with_suffix(f".{os.getpid()}.tmp")
-        temporary.write_text(json.dumps({"version": _TUNING_VERSION, "configs": _tuned}, indent=1), encoding="utf-8")
-        os.replace(temporary, _TUNING_PATH)  # ranks of a multi-GPU job write the same file
+        scratch.write_text(document, encoding="utf-8")
+        os.replace(scratch, _TUNING_PATH)
     except OSError as error:
         print(f"[WGPKernels-B200] Could not save the INT8 tuning cache {_TUNING_PATH}: {error}")
 
@@ -280,81 +312,102 @@ def _capturing():
     return torch.cuda.is_current_stream_capturing() or torch.compiler.is_compiling()
 
 
+class _ColdTimer:
+    """Times launches on the current stream of `device` with CUDA events, each after a read of twice the L2 size from the library's
+    flush buffer, so that weights come from HBM as they do inside a model.  Without that buffer (allocation failed) launches are timed
+    three in a row after a pause."""
+
+    def __init__(self, device):
+        self.lib, self.device, self.stream = _require(), device, _stream(device)
+        self.bytes = 2 * torch.cuda.get_device_properties(device).L2_cache_size
+        self.cold = self.lib.wq8_l2_flush(device.index, self.bytes, self.stream) == 0
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.lib.wq8_l2_flush_release()
+
+    def ms(self, launch):
+        if self.cold:
+            _check(self.lib.wq8_l2_flush(self.device.index, self.bytes, self.stream))
+            count = 1
+        else:
+            torch.cuda._sleep(1_000_000)
+            count = 3
+        first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        first.record()
+        for _ in range(count):
+            launch()
+        last.record()
+        last.synchronize()
+        return first.elapsed_time(last) / count
+
+
 def _best_of(launches, device):
-    """Best time in ms of each launch(): one warm-up each, then three rounds in alternating order, each timed launch after a read of
-    twice the L2 size from the library's own buffer (cold weights, as inside a model); back-to-back launches without that buffer."""
-    lib = _require()
-    names = list(launches)
-    for name in names:
+    """{name: best ms} of the launch() callables: one untimed call each, then three timed rounds, the order reversed every other round."""
+    order = list(launches)
+    for name in order:
         launches[name]()
-    flush_bytes, stream = 2 * torch.cuda.get_device_properties(device).L2_cache_size, _stream(device)
-    cold = lib.wq8_l2_flush(device.index, flush_bytes, stream) == 0
-    timings = {name: float("inf") for name in names}
-    try:
+    best = dict.fromkeys(order, float("inf"))
+    with _ColdTimer(device) as timer:
         for round_index in range(3):
-            for name in (names if round_index % 2 == 0 else names[::-1]):
-                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                if cold:
-                    _check(lib.wq8_l2_flush(device.index, flush_bytes, stream))
-                else:
-                    torch.cuda._sleep(1_000_000)
-                repeats = 1 if cold else 3
-                start.record()
-                for _ in range(repeats):
-                    launches[name]()
-                end.record()
-                end.synchronize()
-                timings[name] = min(timings[name], start.elapsed_time(end) / repeats)
-    finally:
-        lib.wq8_l2_flush_release()
-    return timings
+            for name in (order if round_index % 2 == 0 else reversed(order)):
+                best[name] = min(best[name], timer.ms(launches[name]))
+    return best
 
 
 def _tuned_config(a, a_lo, sa, b, sb, bias, y, mode):
-    """((variant, split), tuned?) of this shape bucket: cached, else timed on this call's operands (y may be overwritten), else the
-    untuned default while a CUDA graph is captured or a graph is compiled."""
-    (m, k), n = a.shape, b.shape[0]
-    key = f"{mode}|{_rows_bucket(m)}x{n}x{k}|{_device_name(b.device.index)}"
-    config = _cache().get(key)
-    if config is not None:
-        return tuple(config), True
-    candidates = _CANDIDATES[mode]
+    """((variant, split), tuned?) for the bucket of this shape.  Known buckets come from the cache; a mode with one candidate needs no
+    timing; while a CUDA graph is captured or compiled the first candidate is used and nothing is recorded; otherwise the candidates are
+    timed on this call's operands (y is overwritten) and the winner is stored."""
+    rows, n, k = a.shape[0], b.shape[0], a.shape[1]
+    key = "|".join((mode, f"{_rows_bucket(rows)}x{n}x{k}", _device_name(b.device.index)))
+    known = _cache().get(key)
+    if known is not None:
+        return tuple(known), True
+    options = _CANDIDATES[mode]
     if _capturing():
-        return candidates[0], False
-    if len(candidates) == 1:
-        _tuned[key] = list(candidates[0])
-        return candidates[0], True
-    started = time.time()
-    log = not _path_tuning.get()
-    label = f"INT8 GEMM {mode} {m}x{n}x{k}"
-    if log:
-        print(f"[WGPKernels-B200] Autotuning {label}...", flush=True)
-    timings = _best_of({config: (lambda config: lambda: gemm(a, a_lo, sa, b, sb, bias, y.dtype, config[1], config[0], y))(config)
-                        for config in candidates}, b.device)
-    best_ms, best = min((ms, config) for config, ms in timings.items())
-    _tuned[key] = list(best)
+        return options[0], False
+    if len(options) == 1:
+        _tuned[key] = list(options[0])
+        return options[0], True
+    verbose = not _path_tuning.get()
+    what = f"INT8 GEMM {mode} {rows}x{n}x{k}"
+    began = time.time()
+    if verbose:
+        print(f"[WGPKernels-B200] Autotuning {what}...", flush=True)
+
+    def launcher(option):
+        variant, split = option
+        return lambda: gemm(a, a_lo, sa, b, sb, bias, y.dtype, split, variant, y)
+
+    times = _best_of({option: launcher(option) for option in options}, b.device)
+    winner = min(options, key=lambda option: (times[option], option))
+    _tuned[key] = list(winner)
     _save_cache()
-    if log:
-        print(f"[WGPKernels-B200] Selected {label}: variant {best[0]}, split {best[1]} ({best_ms * 1000:.1f} us; tuned in "
-              f"{time.time() - started:.2f} s).", flush=True)
-    return best, True
+    if verbose:
+        print(f"[WGPKernels-B200] Selected {what}: variant {winner[0]}, split {winner[1]} ({times[winner] * 1000:.1f} us; tuned in "
+              f"{time.time() - began:.2f} s).", flush=True)
+    return winner, True
 
 
 _plans = {}  # (mode, M, N, K, device) -> (variant, split, workspace bytes, counter bytes)
 
 
 def _plan(a, a_lo, sa, b, sb, bias, y, mode, scratch_output):
-    (m, k), n = a.shape, b.shape[0]
-    shape = (mode, m, n, k, b.device.index)
-    plan = _plans.get(shape)
-    if plan is not None:
-        return plan
-    (variant, split), tuned = _tuned_config(a, a_lo, sa, b, sb, bias, torch.empty_like(y) if scratch_output else y, mode)
-    _require().wq8_gemm_workspace(m, n, k, variant, _sm_count(b.device), split, _sizes)
-    plan = (variant, split, _sizes[0], _sizes[1])
-    if tuned:
-        _plans[shape] = plan
-    return plan
+    """(variant, split, workspace bytes, counter bytes) of a GEMM of this exact shape; remembered once it comes from a tuned choice.
+    scratch_output: y holds data the caller still needs (a residual), so the tuner gets an output of its own."""
+    signature = (mode, a.shape[0], b.shape[0], a.shape[1], b.device.index)
+    if signature in _plans:
+        return _plans[signature]
+    target = torch.empty_like(y) if scratch_output else y
+    (variant, split), final = _tuned_config(a, a_lo, sa, b, sb, bias, target, mode)
+    _require().wq8_gemm_workspace(a.shape[0], b.shape[0], a.shape[1], variant, _sm_count(b.device), split, _sizes)
+    result = (variant, split, _sizes[0], _sizes[1])
+    if final:
+        _plans[signature] = result
+    return result
 
 
 def _weight_scale_groups(sb):
@@ -434,46 +487,50 @@ def _stream_planes(lib, x, weight, scale, bias, residual, residual_scale, y):
     return True
 
 
+def _few_token_call(entry, x, weight, scale, bias, residual, residual_scale, out, extra):
+    """Common part of the few-token entry points: output allocation, the digit-plane kernel when the shape is its own, else `entry` of
+    the C ABI with `extra(m, n, k)` = the arguments between the dtype and the stream."""
+    lib = _require()
+    tokens, k = x.shape
+    channels = weight.shape[0]
+    y = out if out is not None else torch.empty((tokens, channels), dtype=x.dtype, device=x.device)
+    if not _stream_planes(lib, x, weight, scale, bias, residual, residual_scale, y):
+        stream = _stream(x.device)
+        _check(getattr(lib, entry)(x.data_ptr(), x.stride(0), weight.data_ptr(), scale.data_ptr(), _ptr(bias), _ptr(residual),
+                                   _ptr(residual_scale), y.data_ptr(), tokens, channels, k, _DTYPES[x.dtype], *extra(tokens, channels, k, stream), stream))
+    return y
+
+
 def small(x, weight, scale, bias=None, residual=None, residual_scale=None, out=None):
     """Weight-only INT8 for at most 32 tokens: unquantized activations, FP32 accumulation.  K multiple of 64."""
-    lib = _require()
-    m, k = x.shape
-    n = weight.shape[0]
-    sms = _sm_count(x.device)
-    y = torch.empty((m, n), dtype=x.dtype, device=x.device) if out is None else out
-    if _stream_planes(lib, x, weight, scale, bias, residual, residual_scale, y):
-        return y
-    lib.wq8_small_workspace(m, n, k, sms, _sizes)
-    slots = torch.empty(_sizes[0] // 4, dtype=torch.float32, device=x.device) if _sizes[0] else None
-    stream = _stream(x.device)
-    counters = _zeroed_counters(x.device, _sizes[1], stream).data_ptr() if _sizes[1] else None
-    _check(lib.wq8_small(x.data_ptr(), x.stride(0), weight.data_ptr(), scale.data_ptr(), _ptr(bias), _ptr(residual), _ptr(residual_scale),
-                         y.data_ptr(), m, n, k, _DTYPES[x.dtype], sms, _ptr(slots), counters, stream))
-    return y
+    keep = []  # the scratch must outlive the launch call
+
+    def scratch(tokens, channels, k, stream):
+        sms = _sm_count(x.device)
+        _require().wq8_small_workspace(tokens, channels, k, sms, _sizes)
+        slot_bytes, counter_bytes = _sizes[0], _sizes[1]
+        slots = torch.empty(slot_bytes // 4, dtype=torch.float32, device=x.device) if slot_bytes else None
+        keep.append(slots)
+        counters = _zeroed_counters(x.device, counter_bytes, stream).data_ptr() if counter_bytes else None
+        return sms, _ptr(slots), counters
+
+    return _few_token_call("wq8_small", x, weight, scale, bias, residual, residual_scale, out, scratch)
 
 
 def gemv_lines(x, weight, scale, bias=None, residual=None, residual_scale=None, out=None):
     """One to four tokens, unquantized activations (K multiple of 4)."""
-    lib = _require()
-    m, k = x.shape
-    y = torch.empty((m, weight.shape[0]), dtype=x.dtype, device=x.device) if out is None else out
-    if _stream_planes(lib, x, weight, scale, bias, residual, residual_scale, y):
-        return y
-    _check(lib.wq8_gemv_lines(x.data_ptr(), x.stride(0), weight.data_ptr(), scale.data_ptr(), _ptr(bias), _ptr(residual), _ptr(residual_scale),
-                              y.data_ptr(), m, weight.shape[0], k, _DTYPES[x.dtype], _stream(x.device)))
-    return y
+    return _few_token_call("wq8_gemv_lines", x, weight, scale, bias, residual, residual_scale, out, lambda *shape: ())
 
 
 def linear_prepared(prepared, weight, scale, bias=None, residual=None, residual_scale=None, out=None):
     """Y = prepared @ (weight * scale).T + bias (or residual + residual_scale * (...)); weight: INT8 (N, K) matrix or a row range of one."""
-    if prepared.path in ("lines", "small") and scale.dim() == 2:
+    few_tokens = {"lines": gemv_lines, "small": small}.get(prepared.path)
+    if few_tokens is None:
+        return gemm(prepared.x, prepared.lo, prepared.scale, weight, scale, bias, prepared.dtype, out=out, mode=prepared.path,
+                    residual=residual, residual_scale=residual_scale)
+    if scale.dim() == 2:
         raise ValueError("Weights with per-(n, k-block) scales run the 'block' or 'exact' path")
-    if prepared.path == "lines":
-        return gemv_lines(prepared.x, weight, scale, bias, residual, residual_scale, out)
-    if prepared.path == "small":
-        return small(prepared.x, weight, scale, bias, residual, residual_scale, out)
-    return gemm(prepared.x, prepared.lo, prepared.scale, weight, scale, bias, prepared.dtype, out=out, mode=prepared.path, residual=residual,
-                residual_scale=residual_scale)
+    return few_tokens(prepared.x, weight, scale, bias, residual, residual_scale, out)
 
 
 def linear_prepared_segments(prepared, weights, scales, biases, outputs):
@@ -486,84 +543,111 @@ def linear_prepared_segments(prepared, weights, scales, biases, outputs):
 # ---------------------------------------------------------------------------------------------------------------------
 # whole linear and the path policy
 # ---------------------------------------------------------------------------------------------------------------------
+def _chunk_rows(k, mode):
+    """Rows whose quantized copy (codes, the low part of 'exact', scales) stays within SCRATCH_BYTES, a multiple of 128, at least 128."""
+    per_row = k * (2 if mode == "exact" else 1) + 4 * ((k + 127) // 128 if mode == "block" else 1)
+    return max(SCRATCH_BYTES // per_row // 128, 1) * 128
+
+
 def _gemm_path(x, weight, scale, bias, group, mode, act=None, act_weight=None, eps=0.0, residual=None, residual_scale=None, out=None):
-    """'exact', 'block' or 'row' over row chunks whose quantized activations stay within SCRATCH_BYTES."""
-    m, k = x.shape[0], weight.shape[1]
-    out = torch.empty((m, weight.shape[0]), dtype=x.dtype, device=x.device) if out is None else out
-    row_bytes = (2 * k if mode == "exact" else k) + 4 * (-(-k // 128) if mode == "block" else 1)
-    rows = max(128, SCRATCH_BYTES // row_bytes // 128 * 128)
-    for start in range(0, m, rows):
-        stop = min(start + rows, m)
-        prepared = prepare(x[start:stop], group, mode, act, act_weight, eps)
-        rows_out = [t[start:stop] for t in out] if isinstance(out, (list, tuple)) else out[start:stop]
-        linear_prepared(prepared, weight, scale, bias, None if residual is None else residual[start:stop], residual_scale, rows_out)
-        del prepared
+    """'exact', 'block' or 'row': quantize a band of rows, multiply it, next band.  out: a tensor, or a list of destinations."""
+    m, n = x.shape[0], weight.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    several = isinstance(out, (list, tuple))
+    band = _chunk_rows(weight.shape[1], mode)
+    for first in range(0, m, band):
+        rows = slice(first, min(first + band, m))
+        prepared = prepare(x[rows], group, mode, act, act_weight, eps)
+        linear_prepared(prepared, weight, scale, bias, residual[rows] if residual is not None else None, residual_scale,
+                        [t[rows] for t in out] if several else out[rows])
+        del prepared  # the band's codes go back to the allocator before the next band is quantized
     return out
 
 
 def _run(path, x, weight, scale, bias, group, act=None, act_weight=None, eps=0.0, residual=None, residual_scale=None, out=None):
-    if path in ("lines", "small"):
-        return linear_prepared(prepare(x, group, path, act, act_weight, eps), weight, scale, bias, residual, residual_scale, out)
-    return _gemm_path(x, weight, scale, bias, group, path, act, act_weight, eps, residual, residual_scale, out)
+    if path not in ("lines", "small"):
+        return _gemm_path(x, weight, scale, bias, group, path, act, act_weight, eps, residual, residual_scale, out)
+    return linear_prepared(prepare(x, group, path, act, act_weight, eps), weight, scale, bias, residual, residual_scale, out)
+
+
+def _few_token_paths(m, k, groups, line_rows, small_rows):
+    """The few-token kernels that can take this shape, given the row limits in force (group-scaled weights have none)."""
+    if groups:
+        return []
+    usable = []
+    if m <= line_rows and k % 4 == 0:
+        usable.append("lines")
+    if m <= small_rows and k % 64 == 0:
+        usable.append("small")
+    return usable
 
 
 def _precise_paths(m, k, groups=False):
-    """Full-precision candidates; group-scaled weights only have 'exact'."""
-    candidates = []
-    if m <= LINE_MAX_ROWS and k % 4 == 0 and not groups:
-        candidates.append("lines")
-    if m <= SMALL_MAX_ROWS and k % 64 == 0 and not groups:
-        candidates.append("small")
-    return candidates + ["exact"]
+    """Full-precision candidates, 'exact' last (it always applies)."""
+    return _few_token_paths(m, k, groups, LINE_MAX_ROWS, SMALL_MAX_ROWS) + ["exact"]
 
 
 def _static_path(m, k, precise, groups=False):
-    if m <= LINE_ROWS and k % 4 == 0 and not groups:
-        return "lines"
-    if m <= SMALL_ROWS and k % 64 == 0 and not groups:
-        return "small"
+    """The untimed choice (CUDA graph capture, compilation): fixed row thresholds."""
+    few = _few_token_paths(m, k, groups, LINE_ROWS, SMALL_ROWS)
+    if few:
+        return few[0]
     return "exact" if precise or m <= EXACT_ROWS else "block"
 
 
 _paths = {}  # (M, N, K, group, act, precise, device, grouped weights) -> path
 
 
+def _path_key(m, n, k, group, act, precise, groups, device_index):
+    parts = ["path+precise" if precise else "path", f"{_path_bucket(m)}x{n}x{k}", f"g{group}"]
+    if act:
+        parts.append(act)
+    if groups:
+        parts.append("wgroups")
+    parts.append(_device_name(device_index))
+    return "|".join(parts)
+
+
 def choose_path(x, weight, scale, bias=None, group=0, precise=False, act=None, act_weight=None, eps=0.0):
     """The fastest full-precision path while it costs at most EXACT_TOLERANCE more than 'block' (always one with precise=True), timed on
     this call's input once per GPU, shape, input operation and token-count bucket."""
-    (m, k), n = (x.shape[0], weight.shape[1]), weight.shape[0]
-    if m > DECIDE_MAX_ROWS and not precise:
-        return "block"
+    m, n, k = x.shape[0], weight.shape[0], weight.shape[1]
+    if not precise and m > DECIDE_MAX_ROWS:
+        return "block"  # long inputs: the few-token and two-pass paths cannot win
     groups = _weight_scale_groups(scale)
-    shape = (m, n, k, group, act, precise, x.device.index, groups)
-    path = _paths.get(shape)
-    if path is not None:
-        return path
-    key = (f"path{'+precise' if precise else ''}|{_path_bucket(m)}x{n}x{k}|g{group}{f'|{act}' if act else ''}{'|wgroups' if groups else ''}"
-           f"|{_device_name(x.device.index)}")
-    path = _cache().get(key)
-    if path is not None:
-        _paths[shape] = path
-        return path
+    exact_shape = (m, n, k, group, act, precise, x.device.index, groups)
+    if exact_shape in _paths:
+        return _paths[exact_shape]
+    key = _path_key(m, n, k, group, act, precise, groups, x.device.index)
+    stored = _cache().get(key)
+    if stored is not None:
+        _paths[exact_shape] = stored
+        return stored
     if _capturing():
         return _static_path(m, k, precise, groups)
-    candidates = _precise_paths(m, k, groups) + ([] if precise else ["block"])
-    label = f"INT8 path {m}x{n}x{k}{f' ConvRot {group}' if group else ''}{f' {act}' if act else ''}{' (precise)' if precise else ''}"
-    started = time.time()
-    print(f"[WGPKernels-B200] Autotuning {label}...", flush=True)
-    token = _path_tuning.set(True)
+    full_precision = _precise_paths(m, k, groups)
+    contenders = full_precision if precise else full_precision + ["block"]
+    what = f"INT8 path {m}x{n}x{k}" + (f" ConvRot {group}" if group else "") + (f" {act}" if act else "") + (" (precise)" if precise else "")
+    began = time.time()
+    print(f"[WGPKernels-B200] Autotuning {what}...", flush=True)
+
+    def runner(candidate):
+        return lambda: _run(candidate, x, weight, scale, bias, group, act, act_weight, eps)
+
+    quiet = _path_tuning.set(True)  # the tile tuners that run inside these launches keep silent
     try:
-        timings = _best_of({path: (lambda path: lambda: _run(path, x, weight, scale, bias, group, act, act_weight, eps))(path) for path in candidates},
-                           x.device)
+        times = _best_of({candidate: runner(candidate) for candidate in contenders}, x.device)
     finally:
-        _path_tuning.reset(token)
-    full_ms, path = min((timings[p], p) for p in candidates if p != "block")
-    if not precise and full_ms > (1 + EXACT_TOLERANCE) * timings["block"]:
-        path = "block"
-    _tuned[key] = _paths[shape] = path
+        _path_tuning.reset(quiet)
+    chosen = min(full_precision, key=lambda candidate: (times[candidate], candidate))
+    if not precise and times[chosen] > times["block"] * (1 + EXACT_TOLERANCE):
+        chosen = "block"
+    _tuned[key] = chosen
+    _paths[exact_shape] = chosen
     _save_cache()
-    print(f"[WGPKernels-B200] Selected {label}: {path} ({timings[path] * 1000:.1f} us; tuned in {time.time() - started:.2f} s).", flush=True)
-    return path
+    print(f"[WGPKernels-B200] Selected {what}: {chosen} ({times[chosen] * 1000:.1f} us; tuned in {time.time() - began:.2f} s).", flush=True)
+    return chosen
 
 
 def linear(x, weight, scale, bias=None, group=0, precise=False, mode=None, act=None, act_weight=None, eps=0.0, residual=None, residual_scale=None,
@@ -580,72 +664,97 @@ def linear(x, weight, scale, bias=None, group=0, precise=False, mode=None, act=N
 # ---------------------------------------------------------------------------------------------------------------------
 # known-answer test
 # ---------------------------------------------------------------------------------------------------------------------
-def _reference(x, w, s, bias, group, act, act_weight, eps, residual, residual_scale, round_input):
-    """FP32 PyTorch statement of linear() on x's device; round_input rounds op(x) to x's dtype as the few-token paths do."""
-    v = x.float()
+def _input_operation(values, act, act_weight, eps):
+    """op(x) in FP32 with PyTorch operators (the known-answer side of selftest)."""
+    functional = torch.nn.functional
+    if act == "rms_norm":
+        normalised = values * (values.square().mean(dim=-1, keepdim=True) + eps).rsqrt()
+        return normalised if act_weight is None else normalised * act_weight.float()
     if act == "swiglu":
-        gate, value = v.chunk(2, dim=-1)
-        v = torch.nn.functional.silu(gate) * value
-    elif act == "rms_norm":
-        v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * (1 if act_weight is None else act_weight.float())
-    elif act == "gelu":
-        v = torch.nn.functional.gelu(v, approximate="tanh")
-    if group:
-        v = _reference_rotation(v, group)
-    if round_input:
-        v = v.to(x.dtype).float()
-    scale = s.repeat_interleave(128, dim=1)[:, :w.shape[1]] if s.dim() == 2 else s[:, None]
-    out = v @ (w.float() * scale).T + bias.float()
-    return out if residual is None else residual.float() + (1 if residual_scale is None else residual_scale.float()) * out
+        half = values.shape[-1] // 2
+        return functional.silu(values[..., :half]) * values[..., half:]
+    if act == "gelu":
+        return functional.gelu(values, approximate="tanh")
+    return values
 
 
 def _reference_rotation(v, group):
-    h = torch.tensor([[1.0, 1, 1, -1], [1, 1, -1, 1], [1, -1, 1, 1], [-1, 1, 1, 1]], device=v.device)
-    rotation = h
-    while rotation.shape[0] < group:
-        rotation = torch.kron(rotation, h)
-    return (v.reshape(v.shape[0], -1, group) @ (rotation * group ** -0.5)).reshape(v.shape)
+    """ConvRot: every run of `group` values times the Kronecker power of the 4 x 4 block (ones with -1 on the anti-diagonal), scaled to
+    be orthonormal."""
+    block = torch.ones(4, 4, device=v.device) - 2 * torch.eye(4, device=v.device).flip(1)
+    matrix = block
+    while matrix.shape[0] < group:
+        matrix = torch.kron(matrix, block)
+    runs = v.reshape(v.shape[0], v.shape[1] // group, group)
+    return (runs @ (matrix / group ** 0.5)).reshape(v.shape)
 
 
-SELFTEST_CASES = ((1, "lines", 0, None, False), (5, "small", 0, None, False), (5, "small", 64, None, False), (40, "exact", 0, None, False),
-                  (40, "block", 256, None, False), (40, "row", 16, None, False), (2, "lines", 0, "swiglu", True), (5, "small", 64, "rms_norm", True),
-                  (40, "exact", 256, "rms_norm", False), (40, "block", 0, "swiglu", True), (40, "block", 16, "rms_norm", True),
-                  (40, "exact", 64, None, True), (3, "lines", 64, "gelu", False), (5, "small", 0, "gelu", True), (40, "exact", 16, "gelu", False),
-                  (40, "block", 256, "gelu", True), (40, "exact+g", 0, None, True), (40, "block+g", 64, "rms_norm", False),
-                  (40, "block+g", 0, None, True))
+def _reference(x, w, s, bias, group, act, act_weight, eps, residual, residual_scale, round_input):
+    """FP32 PyTorch statement of linear() on x's device; round_input rounds op(x) to x's dtype as the few-token paths do."""
+    prepared = _input_operation(x.float(), act, act_weight, eps)
+    if group:
+        prepared = _reference_rotation(prepared, group)
+    if round_input:
+        prepared = prepared.to(x.dtype).float()
+    per_element = s[:, None] if s.dim() == 1 else s.repeat_interleave(128, dim=1)[:, :w.shape[1]]
+    result = prepared @ (w.float() * per_element).T + bias.float()
+    if residual is None:
+        return result
+    return residual.float() + result * (1 if residual_scale is None else residual_scale.float())
+
+
+# The known-answer cases, grouped by what they exercise: (rows, path, rotation group, input operation, residual?).  The list covers the
+# same kernels, rotations, input operations and residual forms as the reference's selftest, in its order (the random stream is shared).
+_PLAIN_CASES = [(1, "lines", 0, None, False), (5, "small", 0, None, False), (5, "small", 64, None, False), (40, "exact", 0, None, False),
+                (40, "block", 256, None, False), (40, "row", 16, None, False)]
+_FUSED_CASES = [(2, "lines", 0, "swiglu", True), (5, "small", 64, "rms_norm", True), (40, "exact", 256, "rms_norm", False),
+                (40, "block", 0, "swiglu", True), (40, "block", 16, "rms_norm", True), (40, "exact", 64, None, True)]
+_GELU_CASES = [(3, "lines", 64, "gelu", False), (5, "small", 0, "gelu", True), (40, "exact", 16, "gelu", False), (40, "block", 256, "gelu", True)]
+_GROUP_SCALE_CASES = [(40, "exact+g", 0, None, True), (40, "block+g", 64, "rms_norm", False), (40, "block+g", 0, None, True)]
+SELFTEST_CASES = tuple(_PLAIN_CASES + _FUSED_CASES + _GELU_CASES + _GROUP_SCALE_CASES)
+_SELFTEST_VARIANT = {"row": 0, "exact": 1, "block": 10, "block+g": 12, "exact+g": 14}
+_FULL_PRECISION = ("lines", "small", "exact", "exact+g")
 
 
 def selftest(device=None):
     """Runs every kernel once on small inputs with fixed configurations (no tuning): None when the results match PyTorch, else a reason.
-    Same case list and pass bars as the reference's selftest (relative Frobenius error 5e-3 on the full-precision paths, 3e-2 on
-    'block' / 'row')."""
+    Pass bars as in the reference's selftest: relative Frobenius error 5e-3 on the full-precision paths, 3e-2 on 'block' / 'row'."""
     _require()
-    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    generator = torch.Generator(device=device).manual_seed(0)
-    variants = {"exact": 1, "block": 10, "row": 0, "exact+g": 14, "block+g": 12}
+    device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    rng = torch.Generator(device=device).manual_seed(0)
+    n, k, eps = 96, 256, 1e-6
+
+    def normal(*shape, dtype):
+        return torch.randn(*shape, dtype=dtype, device=device, generator=rng)
+
+    def uniform(*shape):
+        return torch.rand(*shape, device=device, generator=rng)
+
     for dtype in (torch.bfloat16, torch.float16):
-        w = torch.randint(-127, 128, (96, 256), dtype=torch.int8, device=device, generator=generator)
-        s = torch.rand(96, device=device, generator=generator) / 127
-        s_groups = torch.rand(96, 2, device=device, generator=generator) / 127
-        bias = torch.randn(96, dtype=dtype, device=device, generator=generator)
-        norm_weight = (torch.rand(256, device=device, generator=generator) + 0.5).to(dtype)
-        for m, path, group, act, with_residual in SELFTEST_CASES:
-            x = torch.randn(m, 512 if act == "swiglu" else 256, dtype=dtype, device=device, generator=generator)
+        weight = torch.randint(-127, 128, (n, k), dtype=torch.int8, device=device, generator=rng)
+        channel_scale = uniform(n) / 127
+        block_scale = uniform(n, k // 128) / 127
+        bias = normal(n, dtype=dtype)
+        norm_weight = (uniform(k) + 0.5).to(dtype)
+        for rows, path, group, act, with_residual in SELFTEST_CASES:
+            x = normal(rows, 2 * k if act == "swiglu" else k, dtype=dtype)
             act_weight = norm_weight if act == "rms_norm" else None
-            residual = torch.randn(m, 96, dtype=dtype, device=device, generator=generator) * 4 if with_residual else None
-            residual_scale = torch.rand(96, dtype=dtype, device=device, generator=generator) if with_residual else None
-            scale = s_groups if path.endswith("+g") else s
-            ref = _reference(x, w, scale, bias, group, act, act_weight, 1e-6, residual, residual_scale, path in ("lines", "small"))
-            prepared = prepare(x, group, path.removesuffix("+g"), act, act_weight, 1e-6)
-            if path in ("lines", "small"):
-                y = linear_prepared(prepared, w, scale, bias, residual, residual_scale, residual)
+            residual = normal(rows, n, dtype=dtype) * 4 if with_residual else None
+            residual_scale = uniform(n).to(dtype) if with_residual else None
+            scale = block_scale if path.endswith("+g") else channel_scale
+            few_tokens = path in ("lines", "small")
+            expected = _reference(x, weight, scale, bias, group, act, act_weight, eps, residual, residual_scale, few_tokens)
+            prepared = prepare(x, group, path.split("+")[0], act, act_weight, eps)
+            if few_tokens:
+                got = linear_prepared(prepared, weight, scale, bias, residual, residual_scale, residual)  # in place when there is a residual
             else:
-                y = gemm(prepared.x, prepared.lo, prepared.scale, w, scale, bias, dtype, 0, variants[path], out=residual, residual=residual,
-                         residual_scale=residual_scale)
-            error = ((y.float() - ref).norm() / ref.norm()).item()
-            if not error < (5e-3 if path in ("lines", "small", "exact", "exact+g") else 3e-2):
-                return (f"{path} kernel mismatch ({dtype}, {m} rows, group {group}, {act or 'no input op'}{', residual' if with_residual else ''}): "
-                        f"relative error {error:.3g}")
+                got = gemm(prepared.x, prepared.lo, prepared.scale, weight, scale, bias, dtype, 0, _SELFTEST_VARIANT[path], out=residual,
+                           residual=residual, residual_scale=residual_scale)
+            error = float((got.float() - expected).norm() / expected.norm())
+            bar = 5e-3 if path in _FULL_PRECISION else 3e-2
+            if not error < bar:
+                details = [str(dtype), f"{rows} rows", f"group {group}", act or "no input op"] + (["residual"] if with_residual else [])
+                return f"{path} kernel mismatch ({', '.join(details)}): relative error {error:.3g}"
     torch.cuda.synchronize(device)
     return None
 
