@@ -69,7 +69,7 @@ def test_unwritable_cache_is_reported_not_raised(tuner, capsys):
 
 
 def test_many_rows_take_block_without_timing(tuner):
-    x, w, s = operands(5000)
+    x, w, s = operands(140000)
     assert tuner.choose_path(x, w, s) == "block"
     assert tuner.calls == []
     tuner.fake.times = {"exact": 2.0}

@@ -30,7 +30,10 @@ SCRATCH_BYTES = 1 << 30
 MAX_GRID_Y = 65535  # kept for callers that chunk rows themselves; this library's quantizers take any row count
 EXACT_TOLERANCE = 0.10
 EXACT_ROWS, LINE_ROWS, SMALL_ROWS = 64, 2, 16            # untimed choices (CUDA graph capture, compilation)
-LINE_MAX_ROWS, SMALL_MAX_ROWS, DECIDE_MAX_ROWS = 4, 32, 4096
+# Up to DECIDE_MAX_ROWS rows the path is timed.  The reference stops at 4096 (on its GPUs the two-pass 'exact' path cannot catch up with
+# 'block' on long inputs); here 'exact' accumulates over all of K in tensor memory and has no per-block work on the CUDA cores, which
+# makes it as fast as 'block' on video-length inputs (measured on B200), so those are timed as well.
+LINE_MAX_ROWS, SMALL_MAX_ROWS, DECIDE_MAX_ROWS = 4, 32, 1 << 17
 ACTS = {None: 0, "rms_norm": 1, "swiglu": 2, "gelu": 3}
 ABI = 11
 _COUNTERS = 1024
