@@ -349,8 +349,8 @@ def main():
         peak, peak_source = 2 * peaks["bf16_tflops_sustained"], "2 x MEASURED_PEAKS bf16_tflops_sustained (INT8 MMA rate = 2 x BF16), of measured"
     else:
         peak, peak_source = 2 * 1400.0, "2 x 1.4 PFLOP/s sustained bf16, of fallback"
-    # DRAM bytes of one GEMM launch: the ncu capture of the same kernel at M = 4096 rows of c1 (dram__bytes_read + write = 275.2 MB,
-    # profiles/gemm_i8_tc_block_c1_rows4096.md) scaled by the rows: codes once, weights once per band of 2048 rows, outputs once.
+    # DRAM bytes of one GEMM launch: the ncu capture of the same kernel at M = 4096 rows of c1 (dram__bytes_read + write = 275.2 MB, its
+    # summary is committed under profiles/) scaled by the rows: codes once, weights once per band of 2048 rows, outputs once.
     traffic, traffic_source = None, None
     if name == "c1" and world == 1:
         traffic = 275.245e6 * m / 4096
