@@ -67,6 +67,28 @@ def _rank_main(rank, world_size, port, failures):
         assert torch.equal(blocked[rank], full[:, layer.start:layer.stop])
         local = layer(c.x, gather=None)
         assert torch.equal(local, full[:, layer.start:layer.stop])
+        # fused gather: the rank's columns go into every rank's full-width buffer (stand-ins for the symmetric-memory views here),
+        # its own buffer first, nothing else is touched
+        views = [torch.zeros(24, 256, dtype=full.dtype) for _ in range(world_size)]
+        order = []
+
+        def writing_linear(x, weight, scale, bias, residual=None, residual_scale=None, out=None, **kwargs):
+            result = cpu_linear(x, weight, scale, bias, residual=residual, residual_scale=residual_scale, **kwargs)
+            for target in out:
+                order.append(next(i for i, view in enumerate(views) if view.data_ptr() == target.data_ptr() - target.storage_offset() * target.element_size()))
+                target.copy_(result)
+            return out
+
+        fused_layer = wdist.ShardedLinear.from_full(c.weight, c.scale, c.bias, linear=writing_linear)
+        fused_layer.symmetric_output = lambda m, dtype, device: (views[rank], views, torch.zeros(1))
+        returned = fused_layer(c.x, gather="fused", out=torch.empty(1))  # a caller's `out` is ignored: the result is the layer's buffer
+        assert returned is views[rank]
+        assert order == [(rank + d) % world_size for d in range(world_size)]
+        for view in views:
+            assert torch.equal(view[:, fused_layer.start:fused_layer.stop], full[:, fused_layer.start:fused_layer.stop])
+            untouched = torch.ones(256, dtype=torch.bool)
+            untouched[fused_layer.start:fused_layer.stop] = False
+            assert not view[:, untouched].any()
         # a shard built from its own slice of a seeded weight equals the slice of the full weight
         w_slice, s_slice = workloads.quantized_weight(128, 5120, 0, n_offset=rank * 128, n_total=5120)
         assert torch.equal(w_slice, workloads.quantized_weight(5120, 5120, 0)[0][rank * 128:(rank + 1) * 128])
