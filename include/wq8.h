@@ -58,7 +58,7 @@ int wq8_rotate_groups(const void* x, void* out, int m, int k, int64_t ldx, int d
  * variant selects the mode (tile shapes are this library's own):
  *   0, 2, 6  'row'      sa (M)               sb (N)
  *   1, 7     'exact'    sa (M), a_lo given   sb (N)
- *   10, 11   'block'    sa (M, ceil(K/128))  sb (N)
+ *   10, 11, 15, 16  'block'  sa (M, ceil(K/128))  sb (N)      (15, 16: tiles of 128 output channels)
  *   12, 13   'block+g'  sa (M, ceil(K/128))  sb (N, ceil(K/128))
  *   14       'exact+g'  sa (M), a_lo given   sb (N, ceil(K/128))
  * a_lo must be non-NULL exactly for variants 1, 7, 14 (else -2).  split: accepted, tiles are never split along K

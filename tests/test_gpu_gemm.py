@@ -11,13 +11,14 @@ from wgpkernels_b200 import workloads
 
 pytestmark = pytest.mark.gpu
 
-MODES = {"row": 0, "exact": 1, "block": 10, "block-cvt": 11, "block+g": 12, "block+g-cvt": 13, "exact+g": 14}
-REF_VARIANT = {"row": 2, "exact": 1, "block": 10, "block-cvt": 10, "block+g": 12, "block+g-cvt": 12, "exact+g": 14}
+MODES = {"row": 0, "exact": 1, "block": 10, "block-cvt": 11, "block-n128": 15, "block-n128-cvt": 16, "block+g": 12, "block+g-cvt": 13, "exact+g": 14}
+REF_VARIANT = {"row": 2, "exact": 1, "block": 10, "block-cvt": 10, "block-n128": 10, "block-n128-cvt": 10, "block+g": 12, "block+g-cvt": 12,
+               "exact+g": 14}
 
 
 def operands(mode, m, n, k, dtype, seed, residual=False):
     """Random INT8 operands with the scale layout of `mode`, on the CPU."""
-    base = mode.removesuffix("-cvt")
+    base = mode.removesuffix("-cvt").removesuffix("-n128")
     kb = -(-k // 128)
     g = torch.Generator().manual_seed(seed)
     a = rand_int8((m, k), seed)

@@ -123,11 +123,11 @@ def test_capture_uses_static_thresholds_and_caches_nothing(tuner, monkeypatch):
 
 def test_tile_tuner_picks_the_fastest_candidate(tuner):
     a, b = torch.zeros(100, 256, dtype=torch.int8), torch.zeros(96, 256, dtype=torch.int8)
-    tuner.fake.times = {(10, 0): 2.0, (11, 0): 1.0}
+    tuner.fake.times = {(10, 0): 2.0, (11, 0): 1.0, (15, 0): 3.0, (16, 0): 3.0}
     config, tuned = tuner._tuned_config(a, None, torch.ones(100, 2), b, torch.ones(96), None, torch.zeros(100, 96), "block")
     assert config == (11, 0) and tuned
     assert tuner._cache()["block|128x96x256|Fake B200"] == [11, 0]
-    tuner.fake.times = {(10, 0): 0.5, (11, 0): 1.0}
+    tuner.fake.times = {(10, 0): 0.5, (11, 0): 1.0, (15, 0): 3.0, (16, 0): 3.0}
     assert tuner._tuned_config(a, None, torch.ones(100, 2), b, torch.ones(96), None, torch.zeros(100, 96), "block")[0] == (11, 0)  # cached
     # a mode with one candidate needs no timing
     before = len(tuner.calls)

@@ -200,7 +200,7 @@ template <int MODE, int BN> struct Shape {
     static constexpr int kAccBuffers = kTmemColumns / kAccColumns;
     static constexpr int kABytes = kBM * kStageK, kBBytes = BN * kStageK;
     static constexpr int kStageBytes = kABytes * (kHilo ? 2 : 1) + kBBytes;
-    static constexpr int kStages = (196 * 1024) / kStageBytes;
+    static constexpr int kStages = (196 * 1024) / kStageBytes > 6 ? 6 : (196 * 1024) / kStageBytes;
     static constexpr int kEpiColumns = BN / 2;  // columns per epilogue thread (two warpgroups split the tile's columns)
     static constexpr int kRingBytes = kWGroup ? kScaleRing * BN * 4 : 0;
     // Output staging: every epilogue warp owns kStoreBuffers buffers of 32 rows x 32 columns of 16-bit outputs (2 KiB each, 64-byte
@@ -208,7 +208,8 @@ template <int MODE, int BN> struct Shape {
     static constexpr int kStoreTile = 32 * 32 * 2;
     // Column parameters of the tile being finished (weight scale as FP32, bias and residual scale in the output type), shared by the epilogue warps.
     static constexpr int kParamBytes = BN * 8;
-    static constexpr int kFixedBytes = kStages * kStageBytes + kRingBytes + kParamBytes + 256 /* barriers, TMEM slot, abort flag */;
+    static constexpr int kBarrierBytes = 384;
+    static constexpr int kFixedBytes = kStages * kStageBytes + kRingBytes + kParamBytes + kBarrierBytes /* barriers, TMEM slot, abort flag */;
     static constexpr int kStoreBuffers = kFixedBytes + kEpilogueWarps * 2 * kStoreTile <= 227 * 1024 ? 2 : 1;
     static constexpr int kStoreBytes = kEpilogueWarps * kStoreBuffers * kStoreTile;
     static constexpr int kSmemBytes = kFixedBytes + kStoreBytes;
@@ -270,14 +271,17 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     T* param_bias = reinterpret_cast<T*>(params + BN * 4);
     T* param_rscale = reinterpret_cast<T*>(params + BN * 6);
     uint64_t* bars = reinterpret_cast<uint64_t*>(params + S::kParamBytes);
-    // barrier layout: full[kStages], empty[kStages], acc_full[2], acc_empty[2], ring_full[kScaleRing], ring_empty[kScaleRing], drained[2],
+    // barrier layout: full[kStages], empty[kStages], acc_full[4], acc_empty[4], ring_full[kScaleRing], ring_empty[kScaleRing], drained[4],
     // params_written, params_consumed; then the TMEM slot and the abort flag
+    constexpr int kMaxAcc = 4;
+    static_assert(kAccBuffers <= kMaxAcc, "accumulator barriers");
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * kStages, bar_acc_full = bar_empty + 8 * kStages,
-                   bar_acc_empty = bar_acc_full + 16, bar_ring_full = bar_acc_empty + 16, bar_ring_empty = bar_ring_full + 8 * kScaleRing,
-                   bar_drained = bar_ring_empty + 8 * kScaleRing, bar_params_written = bar_drained + 16, bar_params_consumed = bar_params_written + 8;
-    static_assert(8 * (2 * kStages + 2 + 2 + 2 * kScaleRing + 2 + 2) <= 224, "barriers overlap the TMEM slot");
-    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(bars) + 224);
-    int& abort_word = *reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 228);
+                   bar_acc_empty = bar_acc_full + 8 * kMaxAcc, bar_ring_full = bar_acc_empty + 8 * kMaxAcc,
+                   bar_ring_empty = bar_ring_full + 8 * kScaleRing, bar_drained = bar_ring_empty + 8 * kScaleRing,
+                   bar_params_written = bar_drained + 8 * kMaxAcc, bar_params_consumed = bar_params_written + 8;
+    static_assert(8 * (2 * kStages + 3 * kMaxAcc + 2 * kScaleRing + 2) <= S::kBarrierBytes - 32, "barriers overlap the TMEM slot");
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(bars) + S::kBarrierBytes - 32);
+    int& abort_word = *reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + S::kBarrierBytes - 28);
     volatile int* abort_flag = &abort_word;
 
     constexpr bool kBiased = S::kFold && FOLD == kFoldBiased && !DUMP;
@@ -291,7 +295,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < kMaxAcc; ++s) {
             mbar_init(bar_acc_full + 8 * s, 1);
             mbar_init(bar_acc_empty + 8 * s, kBiased ? kRearmWarps : kEpilogueWarps);
             mbar_init(bar_drained + 8 * s, kEpilogueWarps);
@@ -392,19 +396,20 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         }
     }
     if (S::kFold && (warp == 1 || warp == 2)) {
-        // ---------------- MMA issuers of the per-block modes: two threads, one per accumulator buffer ----------------
-        // Block g goes to buffer g % 2 and is issued by thread g % 2.  One thread alone spends more time per block on its barrier tests
-        // and commits than the four MMAs run; with two, one thread's bookkeeping overlaps the other one's MMAs.
+        // ---------------- MMA issuers of the per-block modes: two threads ----------------
+        // Block g goes to accumulator buffer g % kAccBuffers (2 buffers of 256 columns, or 4 of 128) and is issued by thread g % 2.  One
+        // thread alone spends more time per block on its barrier tests and commits than the four MMAs run; with two, one thread's
+        // bookkeeping overlaps the other one's MMAs.
         if (lane == 0) {
-            static_assert(!S::kFold || (kStages % 2 == 0 && kAccBuffers == 2), "two issuers alternate over an even number of stages");
+            static_assert(!S::kFold || (kStages % 2 == 0 && kAccBuffers % 2 == 0), "two issuers alternate over even numbers of stages and buffers");
             constexpr uint32_t idesc = instruction_descriptor(BN);
             const int me = warp - 1;
             const int total = ((tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x)) * kblocks;
-            int stage = me;
+            int stage = me, acc = me;
             uint32_t phase = 0, acc_phase = 0;
-            const uint32_t d = tmem_base + me * S::kAccColumns;
             for (int g = me; g < total; g += 2) {
-                if (!mbar_wait(bar_acc_empty + 8 * me, acc_phase ^ 1u, abort_flag, kTimeoutTmemEmpty)) break;
+                const uint32_t d = tmem_base + acc * S::kAccColumns;
+                if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kTimeoutTmemEmpty)) break;
                 if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, kTimeoutFull)) break;
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(smem + stage * S::kStageBytes);
@@ -418,10 +423,11 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     if (S::kHilo) mma_i8(d + BN, a_lo_desc + step, b_desc + step, idesc, accumulate);
                 }
                 tc_commit(bar_empty + 8 * stage);
-                tc_commit(bar_acc_full + 8 * me);
+                tc_commit(bar_acc_full + 8 * acc);
                 stage += 2;
                 if (stage >= kStages) { stage -= kStages; phase ^= 1u; }
-                acc_phase ^= 1u;
+                acc += 2;
+                if (acc >= kAccBuffers) { acc -= kAccBuffers; acc_phase ^= 1u; }
             }
         }
     }
@@ -1026,6 +1032,8 @@ template <class T> static int dispatch(const GemmArgs& g, int variant, cudaStrea
         case 12: return launch<T, kBlockG, 256, kFoldBiased, false>(g, stream);
         case 13: return launch<T, kBlockG, 256, kFoldAdd, false>(g, stream);
         case 14: return launch<T, kExactG, 128, kFoldBiased, false>(g, stream);
+        case 15: return launch<T, kBlock, 128, kFoldBiased, false>(g, stream);  // tiles of 128 columns: four accumulator buffers
+        case 16: return launch<T, kBlock, 128, kFoldAdd, false>(g, stream);
     }
     return -3;
 }

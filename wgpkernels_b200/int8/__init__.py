@@ -257,9 +257,12 @@ def prepare(x, group=0, path="block", act=None, act_weight=None, eps=0.0):
 # ---------------------------------------------------------------------------------------------------------------------
 # (variant, split) candidates per mode; the first is the untuned default.  The variant numbers keep the reference's MODE meaning
 # (row 0/2/6, exact 1/7, block 10/11, block+g 12/13, exact+g 14); what differs between the variants of a mode is this library's own:
-# 10 / 12 convert block sums with the exact magic-number add, 11 / 13 with the conversion instruction.
-_CANDIDATES = {"row": ((0, 0),), "exact": ((1, 0),), "block": ((10, 0), (11, 0)), "exact+g": ((14, 0),), "block+g": ((12, 0), (13, 0))}
-_MODES = {0: "row", 2: "row", 6: "row", 1: "exact", 7: "exact", 10: "block", 11: "block", 12: "block+g", 13: "block+g", 14: "exact+g"}
+# 10 / 12 / 14 keep the accumulators in tensor memory biased for the INT32 -> FP32 conversion, 11 / 13 add the bias with an integer add;
+# 15 / 16 are 10 / 11 with tiles of 128 instead of 256 output channels (four accumulator buffers): the better choice for small products.
+_CANDIDATES = {"row": ((0, 0),), "exact": ((1, 0),), "block": ((10, 0), (11, 0), (15, 0), (16, 0)), "exact+g": ((14, 0),),
+               "block+g": ((12, 0), (13, 0))}
+_MODES = {0: "row", 2: "row", 6: "row", 1: "exact", 7: "exact", 10: "block", 11: "block", 15: "block", 16: "block", 12: "block+g", 13: "block+g",
+          14: "exact+g"}
 _TUNING_VERSION = 1
 _TUNING_PATH = Path(os.environ.get("WGPKERNELS_B200_CACHE") or Path.home() / ".cache" / "wgpkernels_b200" / "int8_tuning.json")
 _tuned = None
