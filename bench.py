@@ -201,6 +201,12 @@ RESULT_STREAM = sys.stdout  # the one JSON line goes here; everything else the p
 
 
 def main():
+    # Libraries under this process write to file descriptor 1 directly (NCCL prints its version there): the descriptor itself is pointed at
+    # stderr and the JSON line goes to a copy of the original stdout.
+    global RESULT_STREAM
+    sys.stdout.flush()
+    RESULT_STREAM = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     sys.stdout = sys.stderr
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
