@@ -216,6 +216,8 @@ def main():
     parser.add_argument("--tokens", type=int, default=1, help="token count of the few-token workloads (c3u, c3d)")
     parser.add_argument("--gather", choices=["fused", "nccl"], default="fused", help="N > 1: how the output slices reach every rank: written "
                         "by the GEMM's tile epilogue into all ranks' buffers (fused), or an NCCL all-gather after the GEMM")
+    parser.add_argument("--mode", choices=["block", "exact", "row"], default="block", help="path of the block workloads (default: the "
+                        "'block' path the headline names; 'exact' is the two-pass full-precision path, 'row' one scale per token)")
     parser.add_argument("--rows", type=int, default=None, help="rows of the block workloads (default: the configuration's own; a smaller "
                         "case of the same shape is what a profiler capture wants)")
     parser.add_argument("--path", default=None, help="path of the few-token workloads: lines, small or exact (default: by token count)")
@@ -258,12 +260,12 @@ def main():
         if in_place:
             g.residual.copy_(residual_master)  # restore the tensor the epilogue overwrites (outside the operator, inside the step)
         if layer is None:
-            return wq.linear(x, g.weight, g.scale, g.bias, mode="block", act=c.act, act_weight=g.act_weight, eps=c.eps, residual=g.residual,
+            return wq.linear(x, g.weight, g.scale, g.bias, mode=args.mode, act=c.act, act_weight=g.act_weight, eps=c.eps, residual=g.residual,
                              residual_scale=g.residual_scale, out=g.residual if in_place else None)
         if args.gather == "fused":  # every rank's GEMM writes its columns into all ranks' (M, N) buffers: no collective on the data
-            return layer(x, gather="fused", mode="block", act=c.act, act_weight=g.act_weight, eps=c.eps, residual=g.residual,
+            return layer(x, gather="fused", mode=args.mode, act=c.act, act_weight=g.act_weight, eps=c.eps, residual=g.residual,
                          residual_scale=g.residual_scale)
-        return layer(x, gather="full", mode="block", act=c.act, act_weight=g.act_weight, eps=c.eps, residual=g.residual,
+        return layer(x, gather="full", mode=args.mode, act=c.act, act_weight=g.act_weight, eps=c.eps, residual=g.residual,
                      residual_scale=g.residual_scale, out=g.residual if in_place else None)
 
     def barrier():
@@ -301,7 +303,7 @@ def main():
     def split_step():
         e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
         e0.record()
-        prepared = wq.prepare(g.x, 0, "block", c.act, g.act_weight, c.eps)
+        prepared = wq.prepare(g.x, 0, args.mode, c.act, g.act_weight, c.eps)
         e1.record()
         wq.linear_prepared(prepared, g.weight, g.scale, g.bias, g.residual, g.residual_scale, g.residual if in_place else None)
         e2.record()
@@ -324,7 +326,7 @@ def main():
             host_linear = HostLinear(g.weight, g.scale, g.bias, chunk_rows=4096)
 
             def e2e_step():
-                host_linear(host_x, host_y, residual=g.residual, residual_scale=g.residual_scale, mode="block", act=c.act,
+                host_linear(host_x, host_y, residual=g.residual, residual_scale=g.residual_scale, mode=args.mode, act=c.act,
                             act_weight=g.act_weight, eps=c.eps)
         else:
             def e2e_step():
@@ -358,23 +360,23 @@ def main():
     # DRAM bytes of one GEMM launch: the ncu capture of the same kernel at M = 4096 rows of c1 (dram__bytes_read + write = 275.2 MB, its
     # summary is committed under profiles/) scaled by the rows: codes once, weights once per band of 2048 rows, outputs once.
     traffic, traffic_source = None, None
-    if name == "c1" and world == 1:
+    if name == "c1" and world == 1 and args.mode == "block":
         traffic = 275.245e6 * m / 4096
         traffic_source = "ncu capture at 4096 rows (275.2 MB) x rows / 4096"
-    local_m_bytes = m * k + 4 * m * ((k + 127) // 128) + (stop - start) * k + 4 * (stop - start) + 2 * m * (stop - start)
+    local_m_bytes = m * k * (2 if args.mode == "exact" else 1) + 4 * m * ((k + 127) // 128 if args.mode == "block" else 1) + (stop - start) * k + 4 * (stop - start) + 2 * m * (stop - start)
     launches_per_step = 2 + (1 if g.scale.dim() == 2 else 0)  # quantizer, GEMM, and the regrouping of group-scaled weight scales
-    quant_bytes = m * k * (2 if c.act != "swiglu" else 4) + m * k + 4 * m * ((k + 127) // 128)
+    quant_bytes = m * k * (2 if c.act != "swiglu" else 4) + m * k * (2 if args.mode == "exact" else 1) + 4 * m * ((k + 127) // 128 if args.mode == "block" else 1)
     line = {
         "metric": METRIC, "value": ops * args.steps / (total_ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "tokens_per_s": m * args.steps / (total_ms * 1e-3),
-        "config": {"workload": f"{name}: {DESCRIPTIONS[name]}", "global_rows": m, "n": n_total, "k": k,
+        "config": {"workload": f"{name}: {DESCRIPTIONS[name]}", "path": args.mode, "global_rows": m, "n": n_total, "k": k,
                    "parallelism": "single GPU" if world == 1 else (f"output channels sharded x{world}, replicated activation, output written into every rank's buffer by the GEMM epilogue (TMA "
                                    "stores over NVLink)" if args.gather == "fused" else
                                    f"output channels sharded x{world}, replicated activation, NCCL all_gather of the output"),
                    "l2": "no flush: the operands of a step (x, q, W, y: > 1 GB) exceed the 126 MB L2"},
         "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
-        "roofline": {"kernel": "gemm_i8_tc (block mode)", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+        "roofline": {"kernel": f"gemm_i8_tc ({args.mode} mode)", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                      "peak_source": peak_source, "nominal_dense_int8_tops": 4500.0, "traffic": traffic, "traffic_source": traffic_source,
                      "algorithmic_bytes": local_m_bytes, "kernel_ms": gemm_ms,
                      "quantizer": {"kernel_ms": quant_ms, "bound": "hbm", "achieved": quant_bytes / (quant_ms * 1e-3) / 1e9, "unit": "GB/s",
