@@ -92,6 +92,20 @@ class ClockSampler:
         return {"sm_mhz": busy[len(busy) // 2], "sm_max_mhz": max_mhz, "samples": len(rows), "power_w_max": power, "reasons": reasons}
 
 
+def tensor_pipe_probe(device, groups=4000):
+    """(INT8 TOPS of the whole GPU, SM MHz, clocks per group of four M128 N256 MMAs) from the probe library built beside the product
+    library: MMAs alone on resident pseudo-random operands, all SMs.  A measurement tool: allocates and synchronizes."""
+    import ctypes
+    from wgpkernels_b200 import build as builder
+    lib = ctypes.CDLL(str(builder.probe_library_file()))
+    lib.wq8_probe_mma_peak.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+    results = (ctypes.c_double * 3)()
+    code = lib.wq8_probe_mma_peak(0, -groups, torch.cuda.get_device_properties(device).multi_processor_count, results)
+    if code:
+        raise RuntimeError(f"tensor-pipe probe failed ({code})")
+    return results[0], results[1], results[2]
+
+
 def cpu_reference_tops(name, rows, repeats):
     """The FP32 dequantize-and-matmul statement of the linear on the host cores, on the first `rows` rows of the workload."""
     from oracle import int8_oracle as oracle
@@ -386,7 +400,7 @@ def main():
     if world == 1:
         # this library's own probe of the INT8 tensor pipe (MMAs alone on resident pseudo-random operands), measured now on this GPU: the
         # ceiling of any kind::i8 kernel at the clocks this board holds under that load
-        probe_tops, probe_mhz, _ = wq.debug_mma_peak("i8", 4000, True)
+        probe_tops, probe_mhz, _ = tensor_pipe_probe(device)
         line["roofline"]["tensor_probe"] = {"int8_tops": probe_tops, "sm_mhz": probe_mhz, "frac": achieved / probe_tops,
                                             "what": "tcgen05 kind::i8 M128 N256 issue rate, all SMs, pseudo-random operands"}
     if not args.no_cpu_baseline and world == 1:

@@ -9,7 +9,7 @@
  *   - all pointers are device pointers owned by the caller unless stated; nothing is allocated here except
  *     the private buffer of wq8_l2_flush();
  *   - `stream` is a raw cudaStream_t of the CURRENT device; calls launch asynchronously and never synchronize;
- *   - return value: 0 = launched, > 0 = a cudaError_t, -1 = bad dtype / act / group, -2 = bad operands,
+ *   - return value: 0 = launched, > 0 = a cudaError_t, -1 = bad dtype / act / group, -2 = bad operands (shape, alignment, NULL),
  *     -3 = unknown variant, -4 = bad segments;
  *   - dtype: 0 = fp16, 1 = bf16, 2 = fp32 (quantizer inputs only, no input operation);
  *   - act: 0 none, 1 rms_norm (act_weight: K values of x's dtype or NULL; eps), 2 swiglu (x rows hold
@@ -58,11 +58,11 @@ int wq8_rotate_groups(const void* x, void* out, int m, int k, int64_t ldx, int d
  * variant selects the mode (tile shapes are this library's own):
  *   0, 2, 6  'row'      sa (M)               sb (N)
  *   1, 7     'exact'    sa (M), a_lo given   sb (N)
- *   10, 11, 15, 16  'block'  sa (M, ceil(K/128))  sb (N)      (15, 16: tiles of 128 output channels)
- *   12, 13   'block+g'  sa (M, ceil(K/128))  sb (N, ceil(K/128))
+ *   10, 11, 15, 16, 20  'block'  sa (M, ceil(K/128))  sb (N)      (15, 16: tiles of 128 output channels; 20: eight drain warps)
+ *   12, 13, 22   'block+g'  sa (M, ceil(K/128))  sb (N, ceil(K/128))   (13: tiles of 128 output channels; 22: eight drain warps)
  *   14       'exact+g'  sa (M), a_lo given   sb (N, ceil(K/128))
  * a_lo must be non-NULL exactly for variants 1, 7, 14 (else -2).  split: accepted, tiles are never split along K
- * here.  workspace / counters: sizes from wq8_gemm_workspace(); variants 12-14 regroup the weight scales by
+ * here.  workspace / counters: sizes from wq8_gemm_workspace(); variants 12-14 and 22 regroup the weight scales by
  * block of K into the workspace (16-byte aligned; NULL is -2), the other variants use neither.  sms: SM count
  * of the device.  Replaces int8_gemm.cu:1648-1656. */
 int wq8_gemm(const int8_t* a, const int8_t* a_lo, const float* sa, const int8_t* b, const float* sb, const void* bias,
@@ -76,21 +76,42 @@ void wq8_gemm_workspace(int m, int n, int k, int variant, int sms, int split, in
 /* Default variant of the 'row' (hilo = 0) or 'exact' (hilo = 1) mode for a shape.  Replaces int8_gemm.cu:1564-1568. */
 int wq8_gemm_select(int m, int n, int k, int hilo, int sms);
 
-/* wq8_gemm of `count` (1 to 4) weights bs[s] (rows, K) of one input in one launch, outputs ys[s] (M, rows),
- * rows a multiple of 8; per-channel weight scales only; no residual.  Here: one launch per weight (same values).  -4 for bad
+/* wq8_gemm of `count` (1 to 4) weights bs[s] (rows, K) of one input in ONE launch that reads the input once, outputs
+ * ys[s] (M, rows) contiguous, rows a multiple of 8; per-channel weight scales only; biases[s] may be NULL; no residual.
+ * A column tile never straddles two weights, so every output equals wq8_gemm's on that weight bit for bit.  -4 for bad
  * segments (count, rows, NULL entries, group-scaled variants).  Replaces int8_gemm.cu:1663-1676. */
 int wq8_gemm_segments(const int8_t* a, const int8_t* a_lo, const float* sa, const int8_t* const* bs, const float* const* sbs,
                       const void* const* biases, void* const* ys, int count, int rows, int m, int k, int dtype, int variant, int sms,
                       int split, int* workspace, int* counters, wq8_stream_t stream);
 
+/* The CUDA-graph-loop forms: the same kernels on a window of rows whose position is read ON THE GPU when the kernel runs
+ * (counter: device pointer to one int64 that a graph's loop body advances), so one captured launch serves every iteration.
+ *   wq8_quantize_at / wq8_quantize_blocks_at: the INPUT rows are rows first + counter[0] * step ... of x; outputs start at row 0.
+ *   wq8_gemm_at: the OUTPUT rows (and the residual's) are rows first + counter[0] * step ... of y; when in_first or in_step is
+ *   non-zero the INPUT rows (a, a_lo and their scales) are rows in_first + counter[0] * in_step ...; span > 0: rscale holds
+ *   scale_step values per span of output rows (a gate per frame), row r reads rscale[(shift + r) / span * scale_step + n].
+ * counter == NULL: exactly the plain entry point.  The buffers must hold every row a counter value can address (rows past the
+ * window are never read or written).  Replace int8_gemm.cu:1396-1402, :1926-1932, :1637-1645 (RowOffset, :238-244). */
+int wq8_quantize_at(const void* x, int8_t* hi, int8_t* lo, float* scale, int m, int k, int64_t ldx, int dtype, int group, int act,
+                    const void* act_weight, float eps, const long long* counter, long long first, long long step, wq8_stream_t stream);
+int wq8_quantize_blocks_at(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, int dtype, int group, int act,
+                           const void* act_weight, float eps, float* inv_rms, const long long* counter, long long first, long long step,
+                           wq8_stream_t stream);
+int wq8_gemm_at(const int8_t* a, const int8_t* a_lo, const float* sa, const int8_t* b, const float* sb, const void* bias,
+                const void* residual, const void* rscale, void* y, int m, int n, int k, int dtype, int variant, int sms, int split,
+                int* workspace, int* counters, const long long* counter, long long first, long long step, long long span,
+                long long scale_step, long long in_first, long long in_step, wq8_stream_t stream);
+
 /* Weight-only INT8 for at most 32 unquantized tokens: Y = X @ (W * sw).T + bias (+ residual), FP32
- * accumulation of exact products.  K multiple of 64.  slots / counters: sizes from wq8_small_workspace();
- * counters zero on entry, left zero.  Replaces int8_gemm.cu:1752-1759 and :1693-1697. */
+ * accumulation of exact products.  K multiple of 64; x and w 16-byte aligned, ldx a multiple of 8 (-2 otherwise).
+ * slots / counters: sizes from wq8_small_workspace(); counters zero on entry, left zero.
+ * Replaces int8_gemm.cu:1752-1759 and :1693-1697. */
 int wq8_small(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
               void* y, int m, int n, int k, int dtype, int sms, float* slots, int* counters, wq8_stream_t stream);
 void wq8_small_workspace(int m, int n, int k, int sms, int64_t* sizes);
 
-/* The same linear for one to four tokens, K multiple of 4, no workspace.  Replaces int8_gemm.cu:1851-1858. */
+/* The same linear for one to four tokens, K multiple of 4, no workspace; x 8-byte aligned, ldx a multiple of 4, w 4-byte
+ * aligned (-2 otherwise).  Replaces int8_gemm.cu:1851-1858. */
 int wq8_gemv_lines(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual,
                    const void* rscale, void* y, int m, int n, int k, int dtype, wq8_stream_t stream);
 
@@ -131,15 +152,16 @@ int wq8_stream_planes(const void* x, int64_t ldx, const int8_t* w, const float* 
  * running during CUDA graph capture or in a section where cudaMalloc is not allowed: none of them can supply the K-split scratch
  * wq8_small asks for.  Here the scratch is a static device buffer inside the library (2 MiB + 4 KiB per GPU that loads it, held until
  * the process exits); nothing is allocated or freed.  The first call on a device looks up the buffer's device address and should come
- * before any stream capture.  Same arguments, values and error codes as wq8_small without `slots` / `counters`; -5 when the shape's
- * scratch exceeds the buffer.  All calls on a device share the buffer: calls whose kernels can overlap on the GPU race. */
+ * before any stream capture.  Same arguments and error codes as wq8_small without `slots` / `counters`, the same kernel choice and so
+ * the same values bit for bit; -5 when the shape's scratch exceeds the buffer.  All calls on a device share the buffer: calls whose
+ * kernels can overlap on the GPU race. */
 int wq8_small_static(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
                      void* y, int m, int n, int k, int dtype, int sms, wq8_stream_t stream);
 
-/* Issue-rate probe of the tensor pipe (kind 0: tcgen05 kind::i8, 1: kind::f16 with BF16): `iters` groups of four M128 N256 MMAs per SM on
- * resident operands (zeros; pseudo-random bytes when iters is negative).  results[0] = TOPS of the whole GPU, [1] = SM MHz during the probe, [2] = clocks per group.  Allocates and frees a
- * small buffer and synchronizes the device: a measurement tool, not part of the linear. */
-int wq8_debug_mma_peak(int kind, int iters, int sms, double* results);
+/* One bounded wait on a barrier that nothing ever completes, with a limit of `clocks` SM clocks (at most 2e9): the kernel writes
+ * 2 to *returned (device int) when the wait gave up (1 if it completed), leaves `code` in the status word that
+ * wq8_debug_status() reads, and returns.  The give-up path that every wait of this library shares, for tests: no fault, no trap. */
+int wq8_debug_wait_probe(long long clocks, int code, int* returned, wq8_stream_t stream);
 
 /* Device-side status word of the GEMM pipeline on the current device: 0, or a code left by a bounded wait
  * that gave up (the kernel then returned early with unspecified output).  Synchronizes the device; clears

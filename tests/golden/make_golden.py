@@ -1,7 +1,7 @@
 """Generates tests/golden/*.npz from the reference's own Python code (run in a container that has the
 reference checkout; the GPU box does not):
 
-    python tests/golden/make_golden.py [/path/to/WGPKernels]
+    python tests/golden/make_golden.py /path/to/WGPKernels
 
 The reference has no golden vectors of its own; its only known-answer check is ``selftest()``
 (wgpkernels/int8/__init__.py:542-576), which compares its kernels with ``_reference`` (:523-539) on a fixed
@@ -23,7 +23,9 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parents[1]))
-REFERENCE = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    sys.exit("usage: python tests/golden/make_golden.py /path/to/WGPKernels   (the reference checkout)")
+REFERENCE = Path(sys.argv[1])
 sys.path.insert(0, str(REFERENCE))
 
 from wgpkernels import int8 as ref  # noqa: E402  (the reference; imports without its CUDA library)

@@ -130,3 +130,38 @@ def test_additions_check_their_arguments(lib):
     assert sizes[0] == 5 * 512 * 4 and sizes[1] == 0
     lib.wq8_gemm_workspace(8, 300, 640, 10, 148, 1, sizes)
     assert sizes[0] == 0 and sizes[1] == 0
+
+
+def test_unaligned_operands_are_refused_not_launched(lib):
+    """Every few-token kernel reads x and w with vector loads: operands that are not aligned for them come back as -2 before any
+    launch (bogus, never dereferenced pointers)."""
+    i, i64, p = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p
+    lib.wq8_small_static.argtypes = [p, i64, p, p, p, p, p, p, i, i, i, i, i, p]
+    aligned, by8, by4, odd = p(4096), p(4096 + 8), p(4096 + 4), p(4096 + 1)
+    # wq8_small and its static-scratch form: x and w 16-byte aligned, row stride a multiple of 8
+    assert lib.wq8_small(aligned, 256, by8, aligned, None, None, None, aligned, 8, 96, 256, 1, 148, None, None, None) == -2
+    assert lib.wq8_small(by8, 256, aligned, aligned, None, None, None, aligned, 8, 96, 256, 1, 148, None, None, None) == -2
+    assert lib.wq8_small(aligned, 252, aligned, aligned, None, None, None, aligned, 8, 96, 256, 1, 148, None, None, None) == -2
+    assert lib.wq8_small_static(aligned, 256, by8, aligned, None, None, None, aligned, 8, 96, 256, 1, 148, None) == -2
+    assert lib.wq8_small_static(by8, 256, aligned, aligned, None, None, None, aligned, 8, 96, 256, 1, 148, None) == -2
+    # wq8_gemv_lines with K % 64 != 0 runs the general kernel: x 8-byte aligned, row stride a multiple of 4, w 4-byte aligned
+    assert lib.wq8_gemv_lines(by4, 100, aligned, aligned, None, None, None, aligned, 2, 96, 100, 1, None) == -2
+    assert lib.wq8_gemv_lines(aligned, 102, aligned, aligned, None, None, None, aligned, 2, 96, 100, 1, None) == -2
+    assert lib.wq8_gemv_lines(aligned, 100, odd, aligned, None, None, None, aligned, 2, 96, 100, 1, None) == -2
+    # and an unaligned w with K % 64 == 0 takes the general kernel only if it is 4-byte aligned
+    assert lib.wq8_gemv_lines(aligned, 256, odd, aligned, None, None, None, aligned, 2, 96, 256, 1, None) == -2
+
+
+def test_row_window_entry_points_check_their_arguments(lib):
+    i, i64, p, ll = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_longlong
+    lib.wq8_gemm_at.argtypes = [p, p, p, p, p, p, p, p, p, i, i, i, i, i, i, i, p, p, p, ll, ll, ll, ll, ll, ll, p]
+    lib.wq8_quantize_at.argtypes = [p, p, p, p, i, i, i64, i, i, i, p, f, p, ll, ll, p]
+    lib.wq8_quantize_blocks_at.argtypes = [p, p, p, i, i, i64, i, i, i, p, f, p, p, ll, ll, p]
+    one = p(16)
+    assert lib.wq8_gemm_at(None, None, None, None, None, None, None, None, None, 0, 96, 256, 1, 10, 148, 0, None, None, one, 0, 1, 0, 0, 0, 0, None) == 0
+    assert lib.wq8_gemm_at(one, None, one, one, one, None, None, None, one, 8, 96, 256, 1, 1, 148, 0, None, None, one, 0, 1, 0, 0, 0, 0, None) == -2   # no low part
+    assert lib.wq8_gemm_at(one, None, one, one, one, None, None, None, one, 8, 96, 256, 1, 10, 148, 0, None, None, one, 0, 1, -1, 0, 0, 0, None) == -2  # span
+    assert lib.wq8_gemm_at(one, None, one, one, one, None, None, None, one, 8, 96, 256, 1, 99, 148, 0, None, None, one, 0, 1, 0, 0, 0, 0, None) == -3
+    assert lib.wq8_quantize_at(None, None, None, None, 0, 256, 256, 1, 0, 0, None, 0.0, one, 0, 1, None) == 0
+    assert lib.wq8_quantize_at(one, one, None, one, 4, 256, 256, 5, 0, 0, None, 0.0, one, 0, 1, None) == -1
+    assert lib.wq8_quantize_blocks_at(one, one, one, 4, 250, 256, 1, 0, 0, None, 0.0, None, one, 0, 1, None) == -2

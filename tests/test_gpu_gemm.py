@@ -11,14 +11,14 @@ from wgpkernels_b200 import workloads
 
 pytestmark = pytest.mark.gpu
 
-MODES = {"row": 0, "exact": 1, "block": 10, "block-cvt": 11, "block-n128": 15, "block-n128-cvt": 16, "block+g": 12, "block+g-cvt": 13, "exact+g": 14}
-REF_VARIANT = {"row": 2, "exact": 1, "block": 10, "block-cvt": 10, "block-n128": 10, "block-n128-cvt": 10, "block+g": 12, "block+g-cvt": 12,
+MODES = {"row": 0, "exact": 1, "block": 10, "block-w8": 20, "block-n128": 15, "block+g": 12, "block+g-w8": 22, "block+g-n128": 13, "exact+g": 14}
+REF_VARIANT = {"row": 2, "exact": 1, "block": 10, "block-w8": 10, "block-n128": 10, "block+g": 12, "block+g-w8": 12, "block+g-n128": 12,
                "exact+g": 14}
 
 
 def operands(mode, m, n, k, dtype, seed, residual=False):
     """Random INT8 operands with the scale layout of `mode`, on the CPU."""
-    base = mode.removesuffix("-cvt").removesuffix("-n128")
+    base = mode.removesuffix("-w8").removesuffix("-n128")
     kb = -(-k // 128)
     g = torch.Generator().manual_seed(seed)
     a = rand_int8((m, k), seed)
@@ -58,7 +58,7 @@ def test_block_sums_extreme_values(wq):
     assert np.array_equal(sums.cpu().numpy(), oracle.block_sums(a.numpy(), b.numpy()))
     sa, sb = torch.ones(m, 4), torch.ones(n)
     y = wq.gemm(a.cuda(), None, sa.cuda(), b.cuda(), sb.cuda(), None, torch.bfloat16, 0, 10)
-    y2 = wq.gemm(a.cuda(), None, sa.cuda(), b.cuda(), sb.cuda(), None, torch.bfloat16, 0, 11)
+    y2 = wq.gemm(a.cuda(), None, sa.cuda(), b.cuda(), sb.cuda(), None, torch.bfloat16, 0, 20)
     expected = oracle.gemm("block", a.numpy(), None, sa.numpy(), b.numpy(), sb.numpy())
     assert torch.equal(y.cpu(), expected) and torch.equal(y2.cpu(), expected)
 
@@ -211,3 +211,79 @@ def test_segments_entry_point(wq):
         assert torch.equal(out, wq.gemm(ga, None, gsa, weight, scale, bias_s, dtype, 0, 10))
     assert lib.wq8_gemm_segments(ga.data_ptr(), None, gsa.data_ptr(), pointers(weights), pointers(scales), pointers(biases), pointers(outputs), 5, rows,
                                  m, k, 1, 10, 148, 0, None, None, wq._stream(ga.device)) == -4
+
+
+def test_segments_through_the_module(wq):
+    """linear_prepared_segments: one launch for the q / k / v weights of one prepared input, 'block' and 'exact', each output equal to
+    linear_prepared on that weight; tiles of 256 and of 128 output channels; rows that are not a multiple of the tile."""
+    assert wq.segments_supported()
+    m, rows, k, dtype = 333, 200, 512, torch.bfloat16
+    x = randn((m, k), dtype, 5).cuda()
+    weights = [rand_int8((rows, k), 60 + s).cuda() for s in range(3)]
+    scales = [(torch.rand(rows, generator=torch.Generator().manual_seed(70 + s)) * 0.01 + 0.001).cuda() for s in range(3)]
+    biases = [randn((rows,), dtype, 80).cuda(), None, randn((rows,), dtype, 82).cuda()]
+    for path in ("block", "exact", "row"):
+        prepared = wq.prepare(x, 0, path)
+        outputs = [torch.full((m, rows), 3.0, dtype=dtype, device="cuda") for _ in range(3)]
+        wq.linear_prepared_segments(prepared, weights, scales, biases, outputs)
+        for weight, scale, bias, out in zip(weights, scales, biases, outputs):
+            zero = torch.zeros(rows, dtype=dtype, device="cuda") if bias is None else bias
+            assert torch.equal(out, wq.linear_prepared(prepared, weight, scale, zero)), path
+    assert wq.debug_status() == 0
+
+
+def _gemm_at(wq, a, a_lo, sa, b, sb, bias, residual, rscale, y, m, variant, counter, first, step, span, scale_step, in_first, in_step):
+    lib = wq._require()
+    n, k = b.shape
+    ptr = lambda t: None if t is None else t.data_ptr()
+    sizes = (__import__("ctypes").c_int64 * 2)()
+    lib.wq8_gemm_workspace(m, n, k, variant, 148, 0, sizes)
+    workspace = torch.empty(max(int(sizes[0]), 16), dtype=torch.uint8, device=a.device)
+    code = lib.wq8_gemm_at(a.data_ptr(), ptr(a_lo), sa.data_ptr(), b.data_ptr(), sb.data_ptr(), ptr(bias), ptr(residual), ptr(rscale), y.data_ptr(), m, n, k,
+                           1, variant, 148, 0, workspace.data_ptr(), None, ptr(counter), first, step, span, scale_step, in_first, in_step,
+                           wq._stream(a.device))
+    assert code == 0, code
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("mode", ["block", "exact", "row", "block+g"])
+def test_gemm_at_row_windows(wq, mode):
+    """wq8_gemm_at: for several values of the device counter, the window of output rows (written in place over the residual, with one
+    residual gate per span of rows) equals the plain GEMM on the matching row slices; rows outside the window are untouched."""
+    dtype, n, k = torch.bfloat16, 264, 640
+    m, total_in, total_out = 300, 900, 1000                      # 300 = 2 tiles + a tail of 44 rows
+    first, step, in_first, in_step, span = 24, 320, 40, 280, 128  # windows: outputs [24 + 320 c, ...), inputs [40 + 280 c, ...)
+    base, a, a_lo, sa, b, sb, bias, _, _ = operands(mode, total_in, n, k, dtype, 17)
+    dev = lambda t: None if t is None else t.cuda()
+    a, a_lo, sa, b, sb, bias = map(dev, (a, a_lo, sa, b, sb, bias))
+    gates = (torch.rand(-(-total_out // span), n, generator=torch.Generator().manual_seed(3)) + 0.5).to(dtype).cuda()
+    untouched = randn((total_out, n), dtype, 19, 4.0).cuda()
+    for count in (0, 1, 2):
+        counter = torch.tensor([count], dtype=torch.int64, device="cuda")
+        out0, in0 = first + count * step, in_first + count * in_step
+        y = untouched.clone()
+        _gemm_at(wq, a, a_lo, sa, b, sb, bias, y, gates, y, m, MODES[mode], counter, first, step, span, n, in_first, in_step)
+        expected = untouched.clone()
+        starts = [out0] + [r for r in range(out0 + 1, out0 + m) if r % span == 0]  # one plain GEMM per span of rows (its gate)
+        for start in starts:
+            stop = min((start // span + 1) * span, out0 + m)
+            rows_in = slice(in0 + start - out0, in0 + stop - out0)
+            expected[start:stop] = wq.gemm(a[rows_in], None if a_lo is None else a_lo[rows_in], sa[rows_in], b, sb, bias, dtype, 0, MODES[mode],
+                                           residual=untouched[start:stop].clone(), residual_scale=gates[start // span].contiguous())
+        assert torch.equal(y, expected), (mode, count, float((y.float() - expected.float()).abs().max()))
+    # no counter: the plain entry point
+    y = torch.empty((m, n), dtype=dtype, device="cuda")
+    _gemm_at(wq, a, a_lo, sa, b, sb, bias, None, None, y, m, MODES[mode], None, 5, 7, 0, 0, 9, 11)
+    assert torch.equal(y, wq.gemm(a[:m], None if a_lo is None else a_lo[:m], sa[:m], b, sb, bias, dtype, 0, MODES[mode]))
+    assert wq.debug_status() == 0
+
+
+def test_bounded_wait_gives_up_and_reports(wq):
+    """A wait on a barrier that nothing completes: the kernel returns by itself, the status word holds the code, and the next GEMM is
+    correct (the context stays usable)."""
+    returned, status = wq.debug_wait_probe(clocks=2_000_000, code=9)
+    assert returned == 2 and status == 9
+    assert wq.debug_status() == 0  # cleared by the read
+    a, b = rand_int8((64, 256), 1), rand_int8((96, 256), 2)
+    sums = wq.debug_block_sums(a.cuda(), b.cuda())
+    assert np.array_equal(sums.cpu().numpy(), oracle.block_sums(a.numpy(), b.numpy())) and wq.debug_status() == 0

@@ -117,21 +117,21 @@ def test_capture_uses_static_thresholds_and_caches_nothing(tuner, monkeypatch):
     assert tuner.choose_path(*operands(2, groups=True)) == "exact"
     assert tuner.calls == [] and tuner._cache() == {} and tuner._paths == {}
     a, b = torch.zeros(100, 256, dtype=torch.int8), torch.zeros(96, 256, dtype=torch.int8)
-    config, tuned = tuner._tuned_config(a, None, torch.ones(100, 2), b, torch.ones(96), None, torch.zeros(100, 96), "block")
+    config, tuned = tuner._tuned_config(100, 96, 256, a.device, "block", lambda option: None)
     assert config == tuner._CANDIDATES["block"][0] and not tuned
 
 
 def test_tile_tuner_picks_the_fastest_candidate(tuner):
     a, b = torch.zeros(100, 256, dtype=torch.int8), torch.zeros(96, 256, dtype=torch.int8)
-    tuner.fake.times = {(10, 0): 2.0, (11, 0): 1.0, (15, 0): 3.0, (16, 0): 3.0}
-    config, tuned = tuner._tuned_config(a, None, torch.ones(100, 2), b, torch.ones(96), None, torch.zeros(100, 96), "block")
-    assert config == (11, 0) and tuned
-    assert tuner._cache()["block|128x96x256|Fake B200"] == [11, 0]
-    tuner.fake.times = {(10, 0): 0.5, (11, 0): 1.0, (15, 0): 3.0, (16, 0): 3.0}
-    assert tuner._tuned_config(a, None, torch.ones(100, 2), b, torch.ones(96), None, torch.zeros(100, 96), "block")[0] == (11, 0)  # cached
+    tuner.fake.times = {(10, 0): 2.0, (20, 0): 2.5, (15, 0): 1.0}
+    config, tuned = tuner._tuned_config(100, 96, 256, a.device, "block", lambda option: None)
+    assert config == (15, 0) and tuned
+    assert tuner._cache()["block|128x96x256|Fake B200"] == [15, 0]
+    tuner.fake.times = {(10, 0): 0.5, (20, 0): 2.5, (15, 0): 1.0}
+    assert tuner._tuned_config(100, 96, 256, a.device, "block", lambda option: None)[0] == (15, 0)  # cached
     # a mode with one candidate needs no timing
     before = len(tuner.calls)
-    assert tuner._tuned_config(a, a, torch.ones(100), b, torch.ones(96), None, torch.zeros(100, 96), "exact") == ((1, 0), True)
+    assert tuner._tuned_config(100, 96, 256, a.device, "exact", lambda option: None) == ((1, 0), True)
     assert len(tuner.calls) == before
     assert set(tuner._MODES[v] for mode, candidates in tuner._CANDIDATES.items() for v, _ in candidates if tuner._MODES[v] != mode) == set()
 

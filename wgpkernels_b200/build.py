@@ -1,6 +1,8 @@
 """Ahead-of-time build of libwgp_int8.so for B200 (sm_100a), written next to the package's `int8` module:
 
-    python -m wgpkernels_b200.build [--output PATH] [--verbose] [--jobs N]
+    python -m wgpkernels_b200.build [--output PATH] [--verbose] [--jobs N] [--force]
+
+A second, tiny library, libwgp_int8_probe.so, is built beside it: the tensor-pipe issue-rate probe that only the benchmark loads.
 
 One architecture only: the GEMM uses tcgen05 / tensor-memory instructions that exist on sm_100a alone, so there is no PTX fallback.
 The CUDA runtime is linked statically and only the C ABI is exported, so the library depends on the driver alone (the same properties
@@ -15,11 +17,17 @@ from pathlib import Path
 
 PACKAGE = Path(__file__).resolve().parent
 SOURCES = ("api.cu", "quantize.cu", "stream.cu", "gemm_tc.cu")
+PROBE_SOURCES = ("probe.cu",)
+HEADERS = ("common.cuh", "tc_ptx.cuh")
 ARCH_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a")
 
 
 def library_file():
     return PACKAGE / "int8" / "libwgp_int8.so"
+
+
+def probe_library_file():
+    return PACKAGE / "int8" / "libwgp_int8_probe.so"
 
 
 def _stale(target, sources):
@@ -29,15 +37,17 @@ def _stale(target, sources):
     return target.stat().st_mtime < newest
 
 
-def build(output=None, nvcc="nvcc", verbose=False, jobs=None, force=False, defines=()):
+def build(output=None, nvcc="nvcc", verbose=False, jobs=None, force=False, sources=SOURCES):
+    """Compiles `sources` into the shared library `output` (default: the product library; the probe library is built with it)."""
+    if output is None and sources is SOURCES:
+        build(probe_library_file(), nvcc, verbose, jobs, force, PROBE_SOURCES)
     target = Path(output or library_file()).resolve()
     csrc = PACKAGE / "csrc"
-    inputs = [csrc / name for name in SOURCES] + [csrc / "common.cuh"]
+    inputs = [csrc / name for name in sources] + [csrc / name for name in HEADERS]
     if not force and not _stale(target, inputs):
         return target
     target.parent.mkdir(parents=True, exist_ok=True)
     common = [nvcc, "-O3", "-std=c++17", "-lineinfo", *ARCH_FLAGS, "-Xcompiler", "-fPIC,-fvisibility=hidden", "--cudart", "static"]
-    common += [f"-D{name}" for name in defines]
     if verbose:
         common += ["-Xptxas", "-v"]
     with tempfile.TemporaryDirectory(prefix="wgpkernels-b200-") as work:
@@ -49,8 +59,8 @@ def build(output=None, nvcc="nvcc", verbose=False, jobs=None, force=False, defin
             if done.returncode:
                 raise RuntimeError(f"nvcc failed on {name}")
             return obj
-        with ThreadPoolExecutor(max_workers=jobs or min(len(SOURCES), os.cpu_count() or 1)) as pool:
-            objects = list(pool.map(compile_one, SOURCES))
+        with ThreadPoolExecutor(max_workers=jobs or min(len(sources), os.cpu_count() or 1)) as pool:
+            objects = list(pool.map(compile_one, sources))
         built = Path(work) / target.name
         subprocess.run([nvcc, "-shared", *ARCH_FLAGS, "--cudart", "static", "-Xcompiler", "-fPIC,-fvisibility=hidden",
                         *map(str, objects), "-o", str(built)], check=True)
@@ -65,9 +75,8 @@ def main():
     parser.add_argument("--verbose", action="store_true", help="print register and shared memory usage (-Xptxas -v)")
     parser.add_argument("--jobs", type=int, default=None)
     parser.add_argument("--force", action="store_true")
-    parser.add_argument("--define", action="append", default=[], help="preprocessor symbol of a diagnostic build (NAME or NAME=VALUE)")
     args = parser.parse_args()
-    print(f"Built {build(args.output, args.nvcc, args.verbose, args.jobs, args.force or bool(args.define), args.define)}")
+    print(f"Built {build(args.output, args.nvcc, args.verbose, args.jobs, args.force)}")
 
 
 if __name__ == "__main__":

@@ -1,10 +1,11 @@
 // INT8 x INT8 -> INT32 GEMM on the 5th-generation tensor cores of sm_100a (tcgen05.mma kind::i8, accumulators in tensor memory),
 // operands staged by TMA (no cluster multicast: every CTA loads its own tiles from its GPU's own memory), warp-specialised:
 //
-//   warp 0      TMA producer: A (and A_lo) 128 x 128-byte tiles, B BN x 128-byte tiles, 128-byte swizzle, ring of STAGES buffers
-//   warp 1      MMA issuer: one elected thread, 4 (x2 with a low part) tcgen05.mma of K = 32 per stage
-//   warps 2-3   tensor-memory allocation; gather of per-(n, k-block) weight scales into a shared-memory ring (group-scaled weights)
-//   warps 4-11  epilogue: tcgen05.ld of the INT32 sums, promotion to FP32, bias / residual, one rounding, stores
+//   warp 0      TMA producer: A (and A_lo) 128 x 128-byte tiles, B BN x 128-byte tiles, 128-byte swizzle, ring of kStages buffers
+//   warps 1-2   MMA issue (one elected thread each): 4 (x2 with a low part) tcgen05.mma of K = 32 per stage; warp 2 owns tensor memory
+//   warp 3      column parameters of the tile being finished (and the per-block weight scales of group-scaled weights) into shared memory
+//   warps 4-19  drain: 16 warps, warp w reads tensor-memory lanes 32 (w % 4) .. + 32 and a quarter of the tile's columns: tcgen05.ld of the
+//               INT32 sums, conversion and promotion to FP32 (two-wide FP32 FMAs), bias / residual, one rounding, TMA stores
 //
 // Modes (the arithmetic of wgpkernels/int8/int8_gemm.cu:773-805 and :836-863 of WGPKernels):
 //   row      INT32 sums over all K; y = fmaf(float(S) * sa[m], sb[n], bias)
@@ -13,185 +14,48 @@
 //   block+g  acc = fmaf(float(S_b), sa[m, b] * sb[n, b], acc); y = acc + bias
 //   exact+g  acc = fmaf(fmaf(float(S_lo_b), 1/254, float(S_hi_b)), sb[n, b], acc); y = fmaf(acc * sa[m], 1, bias)
 // then y = fmaf(y, rscale[n], residual[m, n]) and one rounding.  In the per-block modes the tensor cores produce one exact INT32 block
-// sum per output and 128 of K into a double-buffered tensor-memory accumulator; the epilogue warps drain a buffer (128 x 256 sums) while
-// the MMAs of the next block fill the other one, and keep the FP32 accumulators in registers for the whole tile.
+// sum per output and 128 of K into a multi-buffered tensor-memory accumulator; the drain warps empty a buffer while the MMAs of the
+// next block fill another one, and keep the FP32 accumulators in registers for the whole tile (64 per thread).
 //
 // Every wait is bounded: a wait that gives up records a code in a device status word, raises a CTA-wide abort flag and the CTA leaves
 // through the common exit (tensor memory is always released).
 #include <cuda.h>  // CUtensorMap and its enums only; cuTensorMapEncodeTiled is resolved through the runtime, libcuda is not linked
 
-#include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace wq {
 
 enum Mode : int { kRow = 0, kExact = 1, kBlock = 2, kBlockG = 3, kExactG = 4 };
 
-constexpr int kBM = 128;             // rows of a tile = tensor-memory lanes
-constexpr int kStageK = 128;         // bytes (= INT8 elements) of K per stage: one 128-byte swizzle row, one scale block
-constexpr int kMmaK = 32;            // K of one tcgen05.mma kind::i8
-constexpr int kTmemColumns = 512;    // all of an SM's tensor memory (one CTA per SM)
-constexpr int kEpilogueWarps = 8;
-constexpr int kRearmWarps = 4;       // one per lane quarter of tensor memory: they put the conversion bias back into drained accumulators
-constexpr int kThreads = 32 * (4 + kEpilogueWarps + kRearmWarps);
-// Registers per thread after the split (setmaxnreg): 512 threads are launched with 128 each; the control and re-arm warps keep 40 and
-// the epilogue warps, which hold a tile's FP32 accumulators, take 216: 256 x 40 + 256 x 216 = all 65536.
-constexpr int kSmallRegs = 40, kEpilogueRegs = 216;
+constexpr int kControlWarps = 4;
+// Drain warps: PARTS per lane quarter of tensor memory, each with 1 / PARTS of the tile's columns.  Registers per thread after the split
+// (setmaxnreg): the control warps keep few, the drain warps, which hold a tile's FP32 accumulators, take the rest.
+//   PARTS = 2:  384 threads launched with 168 registers; control 40, drain 216 (128 accumulators + 2 x 32 staging): 128 x 40 + 256 x 216
+//   PARTS = 4:  640 threads launched with 96 registers;  control 32, drain 112 (64 accumulators + 2 x 16 staging):  128 x 32 + 512 x 112
+template <int PARTS> struct Roles {
+    static_assert(PARTS == 2 || PARTS == 4, "two or four drain warps per lane quarter");
+    static constexpr int kDrainWarps = 4 * PARTS;
+    static constexpr int kThreads = 32 * (kControlWarps + kDrainWarps);
+    static constexpr int kControlRegs = PARTS == 2 ? 40 : 32, kDrainRegs = PARTS == 2 ? 216 : 112;
+    static constexpr int kChunk = PARTS == 2 ? 32 : 16;  // columns a drain thread brings in from tensor memory at once
+};
 constexpr int kScaleRing = 4;        // blocks of gathered weight scales in flight
+constexpr int kMaxSegments = 4;      // weights of one launch that share the input (wq8_gemm_segments)
 constexpr long long kWaitLimit = 4000000000ll;  // clocks (about two seconds) before a wait gives up
 
 __device__ int g_status = 0;  // first code of a wait that gave up (wq::Status)
 
-#ifdef WQ_TRACE
-// Diagnostic build only: clock stamps of CTA 0 (MMA issuer at slot 0, first epilogue warp at slot 4096), read back by wq8_debug_trace.
-__device__ long long g_trace[8192];
-#define WQ_STAMP(base, index, field) do { if (blockIdx.x == 0 && (index) < 500) g_trace[(base) + (index) * 8 + (field)] = clock64(); } while (0)
-#else
-#define WQ_STAMP(base, index, field) do {} while (0)
-#endif
-
-// ---- PTX wrappers --------------------------------------------------------------------------------------------------
-WQ_DEVICE uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-WQ_DEVICE void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
-WQ_DEVICE void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-WQ_DEVICE void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
-// One potentially blocking test of the phase: the hardware may suspend the thread for up to `kSuspendNs` (it resumes as soon as the
-// phase completes), so a waiting role does not spend its scheduler's issue slots on polling.
-constexpr uint32_t kSuspendNs = 4000;
-WQ_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity), "r"(kSuspendNs)
-        : "memory");
-    return done != 0;
+WQ_DEVICE bool wait_on(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    return mbar_wait(bar, parity, abort_flag, code, &g_status, kWaitLimit);
 }
 
-// Non-blocking test of the phase: the cheap first look (the phase has usually completed by the time a role asks).
-WQ_DEVICE bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-
-// Waits for the phase of `parity`; false when the CTA is aborting or the wait ran out (then `code` is recorded and the abort flag raised).
-WQ_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-    if (mbar_test(bar, parity)) return true;
-    const long long start = clock64();
-    for (uint32_t spin = 1;; ++spin) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 15u) == 0u) {
-            if (*abort_flag) return false;
-            if (clock64() - start > kWaitLimit) {
-                *abort_flag = code;
-                atomicCAS(&g_status, 0, code);
-                return false;
-            }
-        }
-    }
-}
-
-WQ_DEVICE void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst), "l"(map),
-                 "r"(bar), "r"(x), "r"(y)
-                 : "memory");
-}
-WQ_DEVICE void prefetch_tensormap(const CUtensorMap* map) { asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory"); }
-
-WQ_DEVICE void tmem_alloc(uint32_t slot_in_smem, uint32_t columns) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_in_smem), "r"(columns) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-WQ_DEVICE void tmem_dealloc(uint32_t address, uint32_t columns) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
-}
-WQ_DEVICE void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-WQ_DEVICE void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-// The mbarrier is arrived on once every tcgen05 operation this thread issued before has completed.
-WQ_DEVICE void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// D (tensor memory, 128 lanes x N columns of INT32) = or += A (128 x 32 INT8, smem) * B (N x 32 INT8, smem)^T
-WQ_DEVICE void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// 32 consecutive columns of this thread's lane (a warp reads the 32 lanes of its quarter of tensor memory).
-#define WQ_R4(a, i) "=r"(a[i]), "=r"(a[i + 1]), "=r"(a[i + 2]), "=r"(a[i + 3])
-WQ_DEVICE void tmem_load_32(uint32_t taddr, int* v) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : WQ_R4(v, 0), WQ_R4(v, 4), WQ_R4(v, 8), WQ_R4(v, 12), WQ_R4(v, 16), WQ_R4(v, 20), WQ_R4(v, 24), WQ_R4(v, 28)
-        : "r"(taddr)
-        : "memory");
-}
-#undef WQ_R4
-// Completes the loads issued before it (the toolchain tracks tcgen05.ld destinations until this instruction).
-WQ_DEVICE void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
-WQ_DEVICE uint64_t smem_descriptor(uint32_t address) {
-    uint64_t d = (address & 0x3ffffu) >> 4;       // start address, 16-byte units
-    d |= uint64_t(1) << 16;                       // leading byte offset (unused for swizzled K-major layouts)
-    d |= uint64_t(1024 >> 4) << 32;               // stride byte offset between 8-row groups
-    d |= uint64_t(1) << 46;                       // descriptor version of sm_100
-    d |= uint64_t(2) << 61;                       // 128-byte swizzle
-    return d;
-}
-// Instruction descriptor: INT32 accumulator, signed INT8 A and B, both K-major, M = 128, N = n.
-__host__ __device__ constexpr uint32_t instruction_descriptor(int n) { return (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(kBM >> 4) << 24); }
-
-// v[0..15] twice into the 32 columns starting at taddr of this thread's lane (sixteen source registers stay resident).
-#define WQ_IN4(a, i) "r"(a[i]), "r"(a[i + 1]), "r"(a[i + 2]), "r"(a[i + 3])
-WQ_DEVICE void tmem_store_32(uint32_t taddr, const int* v) {
-#pragma unroll
-    for (int part = 0; part < 2; ++part)
-        asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr + part * 16),
-                     WQ_IN4(v, 0), WQ_IN4(v, 4), WQ_IN4(v, 8), WQ_IN4(v, 12)
-                     : "memory");
-}
-#undef WQ_IN4
-WQ_DEVICE void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// Exact INT32 -> FP32 of block sums.  |sum| <= 128 * 127 * 127 < 2^22, so the bits of 1.5 * 2^23 plus the sum are the float
-// 1.5 * 2^23 + sum exactly and one subtraction recovers the sum (the conversion instruction issues at a quarter of that rate).
-// kFoldBiased: the accumulators in tensor memory START at those bits (the epilogue re-arms every column it drains), so the MMAs
-// themselves deliver the biased value and no integer add is needed.  kFoldAdd: the accumulators start at zero and the bits are added here.
-constexpr int kBiasBits = 0x4B400000;
-#define WQ_B4 kBiasBits, kBiasBits, kBiasBits, kBiasBits
-// The re-arming store takes its 16 source registers from here, through volatile loads: values the compiler cannot rebuild with moves in
-// front of every store (it would: a move per register and store), so they stay resident for the whole kernel.
-__device__ int g_bias_run[16] = {WQ_B4, WQ_B4, WQ_B4, WQ_B4};
-#undef WQ_B4
-WQ_DEVICE void load_bias_run(int* v) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) asm volatile("ld.volatile.global.b32 %0, [%1];" : "=r"(v[j]) : "l"(g_bias_run + j));
-}
-constexpr float kBiasValue = 12582912.f;
-enum Fold : int { kFoldBiased = 0, kFoldAdd = 1 };
-template <int FOLD> WQ_DEVICE float block_sum_to_float(int s) {
-    if constexpr (FOLD == kFoldAdd) s += kBiasBits;
-    return __int_as_float(s) - kBiasValue;
-}
-
-template <int MODE, int BN> struct Shape {
+// INT32 -> FP32 of the block sums: the conversion instruction (exact: |sum| <= 128 * 127 * 127 < 2^24).  It runs on a pipe of its own,
+// beside the FP32 pipe that does the multiply-adds, and needs no preparation of the accumulators: the first MMA of a block overwrites
+// its tensor-memory buffer, so a drain warp hands a buffer back as soon as it has read its columns.  (Accumulators that start at
+// the bits of 1.5 * 2^23, so that one FP32 subtraction converts, cost more than they save: re-arming a buffer from registers takes a
+// register move per column, on the FP32 pipe.)
+template <int MODE, int BN, bool WIDE, int PARTS> struct Shape {
+    static constexpr int kDrainWarps = Roles<PARTS>::kDrainWarps;
     static constexpr bool kHilo = MODE == kExact || MODE == kExactG;
     static constexpr bool kFold = MODE == kBlock || MODE == kBlockG || MODE == kExactG;  // one accumulation per 128 of K
     static constexpr bool kWGroup = MODE == kBlockG || MODE == kExactG;
@@ -200,62 +64,76 @@ template <int MODE, int BN> struct Shape {
     static constexpr int kAccBuffers = kTmemColumns / kAccColumns;
     static constexpr int kABytes = kBM * kStageK, kBBytes = BN * kStageK;
     static constexpr int kStageBytes = kABytes * (kHilo ? 2 : 1) + kBBytes;
-    static constexpr int kStages = (196 * 1024) / kStageBytes > 6 ? 6 : (196 * 1024) / kStageBytes;
-    static constexpr int kEpiColumns = BN / 2;  // columns per epilogue thread (two warpgroups split the tile's columns)
+    static constexpr int kEpiColumns = BN / PARTS;  // columns per drain thread (PARTS warps split the tile's columns)
     static constexpr int kRingBytes = kWGroup ? kScaleRing * BN * 4 : 0;
-    // Output staging: every epilogue warp owns kStoreBuffers buffers of 32 rows x 32 columns of 16-bit outputs (2 KiB each, 64-byte
-    // swizzle) from which the TMA unit writes whole 64-byte row segments; two buffers per warp when shared memory has room for them.
-    static constexpr int kStoreTile = 32 * 32 * 2;
-    // Column parameters of the tile being finished (weight scale as FP32, bias and residual scale in the output type), shared by the epilogue warps.
+    // Output staging: every drain warp owns one buffer of 32 rows x 32 columns of 16-bit outputs (2 KiB, 64-byte swizzle) from which the
+    // TMA unit writes whole 64-byte row segments.  kWide (several destinations): 32 rows x 64 columns (4 KiB, 128-byte swizzle), so that
+    // rows of 128 bytes cross NVLink; one operand stage less fits then.
+    static constexpr bool kWide = WIDE && kEpiColumns >= 64;
+    static constexpr int kStoreTile = kWide ? 32 * 64 * 2 : 32 * 32 * 2;
+    static constexpr int kStoreBytes = kDrainWarps * kStoreTile;
+    // Column parameters of the tile being finished (weight scale as FP32, bias and residual scale in the output type), shared by the drain warps.
     static constexpr int kParamBytes = BN * 8;
     static constexpr int kBarrierBytes = 384;
-    static constexpr int kFixedBytes = kStages * kStageBytes + kRingBytes + kParamBytes + kBarrierBytes /* barriers, TMEM slot, abort flag */;
-    static constexpr int kStoreBuffers = kFixedBytes + kEpilogueWarps * 2 * kStoreTile <= 227 * 1024 ? 2 : 1;
-    static constexpr int kStoreBytes = kEpilogueWarps * kStoreBuffers * kStoreTile;
-    static constexpr int kSmemBytes = kFixedBytes + kStoreBytes;
+    static constexpr int kRoom = 227 * 1024 - kStoreBytes - kRingBytes - kParamBytes - kBarrierBytes;
+    static constexpr int kStages = kRoom / kStageBytes > 6 ? 6 : kRoom / kStageBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kRingBytes + kStoreBytes + kParamBytes + kBarrierBytes;
     static_assert(kAccBuffers >= 1 && kStages >= 2, "tile does not fit");
+    static_assert(kEpiColumns % 32 == 0, "a drain thread works on chunks of 16 or 32 and writes out chunks of 32 columns");
 };
+
+// Row window of a launch made by one of the *_at entry points: the counter lives on the GPU and is read when the kernel runs (a CUDA
+// graph replays the launch while a loop counter advances).  shift = first + counter[0] * step rows of y and of the residual;
+// in_first / in_step the same for A, A_lo and their scales; span > 0: rscale holds scale_step values per span of output rows.
+struct RowWindow { const long long* counter; long long first, step, span, scale_step, in_first, in_step; };
 
 struct GemmParams {
     const float* sa;
-    const float* sb;
-    const void* bias;
+    const float* sb[kMaxSegments];
+    const void* bias[kMaxSegments];
+    void* y[kMaxSegments];
     const void* residual;
     const void* rscale;
-    void* y;
     int* dump;  // debug: raw block sums (kblocks, M, N)
-    int m, n, k;
-    int tiles_m, tiles_n;
+    int m, n, k;    // n: output channels of one segment
+    int tiles_m, tiles_n, seg_tiles;  // tiles_n = segments * seg_tiles: a column tile never straddles two segments
     int vector_io;  // y, residual, sb, bias and rscale allow 16-byte accesses (N multiple of 8, aligned bases)
     const float* sb_blocks;  // group-scaled weights: the scales regrouped by block, (ceil(K/128), n_pad) with zeros past N
     int n_pad;               // row length of sb_blocks: N rounded up to 256
     int tma_y;      // the output maps describe the destinations: whole 32-column chunks leave through shared memory and the TMA unit
-    int wide_store;    // several destinations: the two staging tiles of a warp form one of 32 rows x 64 columns (128-byte rows cross NVLink
-                       // in half as many, twice as large writes); the output maps then have 64-column boxes and the 128-byte swizzle
     int destinations;  // copies of the output written by the TMA stores (1, or one per GPU of an N-sharded layer)
+    int tail_rows;     // row window: rows of the last, partial row tile (its A tile is fetched through the *_tail maps), 0 = none
     int64_t ld_y, ld_residual;  // row strides in elements of y and of the residual
+    RowWindow window;
 };
 
 // Up to eight destinations of the output: the same (M, N) block in this GPU's buffer and, for an N-sharded layer, in the buffers of its
-// peers (ordinary TMA stores over NVLink; nothing is ever loaded from a peer).
+// peers (ordinary TMA stores over NVLink; nothing is ever loaded from a peer).  With segments: map s = the output of weight s.
 constexpr int kMaxDestinations = 8;
 struct OutputMaps { CUtensorMap map[kMaxDestinations]; };
+struct InputMaps { CUtensorMap a, a_lo, a_tail, a_lo_tail; };
+struct WeightMaps { CUtensorMap map[kMaxSegments]; };
 
-struct TileCoord { int m0, n0; };
+struct TileCoord { int m0, n0, segment; };
 // Bands of 16 row tiles are swept over all column tiles, so the CTAs running together share a few A bands and B tiles in L2.
-template <int BN> WQ_DEVICE TileCoord tile_origin(int t, int tiles_m, int tiles_n) {
+template <int BN> WQ_DEVICE TileCoord tile_origin(int t, int tiles_m, int tiles_n, int seg_tiles) {
     constexpr int kBand = 16;
     const int width = kBand * tiles_n, first = (t / width) * kBand;
     const int rows = min(tiles_m - first, kBand);
-    return {(first + (t % width) % rows) * kBM, ((t % width) / rows) * BN};
+    const int column_tile = (t % width) / rows;
+    const int segment = column_tile / seg_tiles;
+    return {(first + (t % width) % rows) * kBM, (column_tile - segment * seg_tiles) * BN, segment};
 }
 
-template <class T, int MODE, int BN, int FOLD, bool DUMP>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b,
-           const __grid_constant__ OutputMaps out_maps, const GemmParams p) {
-    using S = Shape<MODE, BN>;
+WQ_DEVICE float2 as_pair(int a, int b) { return make_float2(__int_as_float(a), __int_as_float(b)); }
+
+template <class T, int MODE, int BN, bool WIDE, bool DUMP, int PARTS>
+__global__ void __launch_bounds__(Roles<PARTS>::kThreads, 1)
+gemm_i8_tc(const __grid_constant__ InputMaps in_maps, const __grid_constant__ WeightMaps w_maps, const __grid_constant__ OutputMaps out_maps,
+           const GemmParams p) {
+    using S = Shape<MODE, BN, WIDE, PARTS>;
     constexpr int kStages = S::kStages, kAccBuffers = S::kAccBuffers, kEpi = S::kEpiColumns;
+    constexpr int kDrainWarps = Roles<PARTS>::kDrainWarps, kControlRegs = Roles<PARTS>::kControlRegs, kDrainRegs = Roles<PARTS>::kDrainRegs;
     // No static shared memory in this kernel: the dynamic block starts at the CTA's shared window, which is 1024-byte aligned (the
     // 128-byte swizzle of the operand stages needs that); a launch that finds it otherwise reports it and does nothing.
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -271,69 +149,60 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     T* param_bias = reinterpret_cast<T*>(params + BN * 4);
     T* param_rscale = reinterpret_cast<T*>(params + BN * 6);
     uint64_t* bars = reinterpret_cast<uint64_t*>(params + S::kParamBytes);
-    // barrier layout: full[kStages], empty[kStages], acc_full[4], acc_empty[4], ring_full[kScaleRing], ring_empty[kScaleRing], drained[4],
-    // params_written, params_consumed; then the TMEM slot and the abort flag
-    constexpr int kMaxAcc = 4;
-    static_assert(kAccBuffers <= kMaxAcc, "accumulator barriers");
-    const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * kStages, bar_acc_full = bar_empty + 8 * kStages,
+    // barrier layout: full[6], empty[6], acc_full[4], acc_empty[4], ring_full[kScaleRing], ring_empty[kScaleRing], params_written,
+    // params_consumed; then the TMEM slot and the abort flag
+    constexpr int kMaxStages = 6, kMaxAcc = 4;
+    static_assert(kAccBuffers <= kMaxAcc && kStages <= kMaxStages, "barrier table");
+    const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * kMaxStages, bar_acc_full = bar_empty + 8 * kMaxStages,
                    bar_acc_empty = bar_acc_full + 8 * kMaxAcc, bar_ring_full = bar_acc_empty + 8 * kMaxAcc,
-                   bar_ring_empty = bar_ring_full + 8 * kScaleRing, bar_drained = bar_ring_empty + 8 * kScaleRing,
-                   bar_params_written = bar_drained + 8 * kMaxAcc, bar_params_consumed = bar_params_written + 8;
-    static_assert(8 * (2 * kStages + 3 * kMaxAcc + 2 * kScaleRing + 2) <= S::kBarrierBytes - 32, "barriers overlap the TMEM slot");
+                   bar_ring_empty = bar_ring_full + 8 * kScaleRing, bar_params_written = bar_ring_empty + 8 * kScaleRing,
+                   bar_params_consumed = bar_params_written + 8;
+    static_assert(8 * (2 * kMaxStages + 2 * kMaxAcc + 2 * kScaleRing + 2) <= S::kBarrierBytes - 32, "barriers overlap the TMEM slot");
     uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(bars) + S::kBarrierBytes - 32);
     int& abort_word = *reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + S::kBarrierBytes - 28);
     volatile int* abort_flag = &abort_word;
 
-    constexpr bool kBiased = S::kFold && FOLD == kFoldBiased && !DUMP;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kblocks = (p.k + kStageK - 1) / kStageK;
     const int tiles = p.tiles_m * p.tiles_n;
+    // row window of the *_at entry points: where the outputs go and where the inputs come from
+    long long out_shift = 0, in_shift = 0;
+    if (p.window.counter) {
+        const long long count = __ldg(p.window.counter);
+        out_shift = p.window.first + count * p.window.step;
+        if (p.window.in_first || p.window.in_step) in_shift = p.window.in_first + count * p.window.in_step;
+    }
 
     if (threadIdx.x == 0) {
         abort_word = 0;
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
         for (int s = 0; s < kMaxAcc; ++s) {
             mbar_init(bar_acc_full + 8 * s, 1);
-            mbar_init(bar_acc_empty + 8 * s, kBiased ? kRearmWarps : kEpilogueWarps);
-            mbar_init(bar_drained + 8 * s, kEpilogueWarps);
+            mbar_init(bar_acc_empty + 8 * s, kDrainWarps);
         }
         mbar_init(bar_params_written, 32);
-        mbar_init(bar_params_consumed, kEpilogueWarps);
+        mbar_init(bar_params_consumed, kDrainWarps);
         for (int s = 0; s < kScaleRing; ++s) {
             mbar_init(bar_ring_full + 8 * s, 1);
-            mbar_init(bar_ring_empty + 8 * s, kEpilogueWarps);
+            mbar_init(bar_ring_empty + 8 * s, kDrainWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        prefetch_tensormap(&map_a);
-        prefetch_tensormap(&map_b);
-        if (S::kHilo) prefetch_tensormap(&map_a_lo);
-        if (p.tma_y)
-            for (int d = 0; d < p.destinations; ++d) prefetch_tensormap(&out_maps.map[d]);
+        prefetch_tensormap(&in_maps.a);
+        prefetch_tensormap(&w_maps.map[0]);
+        if (S::kHilo) prefetch_tensormap(&in_maps.a_lo);
+        if (p.tma_y) prefetch_tensormap(&out_maps.map[0]);
     }
     if (warp == 2) tmem_alloc(smem_u32(&tmem_slot), kTmemColumns);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
-    int bias_run[16];
-    if constexpr (kBiased) {
-        // the re-arm warps put the bias bits into every accumulator column once; from here on they do it after each drain
-        if (warp >= 4 + kEpilogueWarps) {
-            load_bias_run(bias_run);
-            const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
-            for (int column = 0; column < kTmemColumns; column += 32) tmem_store_32(lane_addr + column, bias_run);
-            tmem_store_wait();
-        }
-        tc_fence_before();
-        __syncthreads();
-        tc_fence_after();
-    }
 
-    if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kSmallRegs));
+    if (warp < kControlWarps) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
@@ -341,15 +210,22 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             uint32_t phase = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-                const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n);
+                const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n, p.seg_tiles);
+                // a row window addresses A through maps without a row bound: its last, partial row tile is fetched with a box of just
+                // the rows that exist (the other rows of the stage keep stale bytes; their outputs are never stored)
+                const bool tail = p.tail_rows && c.m0 + kBM > p.m;
+                const CUtensorMap* map_a = tail ? &in_maps.a_tail : &in_maps.a;
+                const CUtensorMap* map_a_lo = tail ? &in_maps.a_lo_tail : &in_maps.a_lo;
+                const uint32_t bytes = tail ? uint32_t(p.tail_rows * kStageK * (S::kHilo ? 2 : 1) + S::kBBytes) : uint32_t(S::kStageBytes);
+                const int a_row = int(in_shift) + c.m0;
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kTimeoutEmpty))) break;
+                    if (!(ok = wait_on(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kTimeoutEmpty))) break;
                     const uint32_t full = bar_full + 8 * stage;
                     const uint32_t dst = smem_u32(smem + stage * S::kStageBytes);
-                    mbar_expect_tx(full, S::kStageBytes);
-                    tma_load_2d(dst, &map_a, full, kb * kStageK, c.m0);
-                    if (S::kHilo) tma_load_2d(dst + S::kABytes, &map_a_lo, full, kb * kStageK, c.m0);
-                    tma_load_2d(dst + S::kABytes * (S::kHilo ? 2 : 1), &map_b, full, kb * kStageK, c.n0);
+                    mbar_expect_tx(full, bytes);
+                    tma_load_2d(dst, map_a, full, kb * kStageK, a_row);
+                    if (S::kHilo) tma_load_2d(dst + S::kABytes, map_a_lo, full, kb * kStageK, a_row);
+                    tma_load_2d(dst + S::kABytes * (S::kHilo ? 2 : 1), &w_maps.map[c.segment], full, kb * kStageK, c.n0);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -371,8 +247,8 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
                 for (int kb = 0; kb < kblocks; ++kb) {
                     const bool new_acc = kb == 0;
-                    if (new_acc && !(ok = mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kTimeoutTmemEmpty))) break;
-                    if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, kTimeoutFull))) break;
+                    if (new_acc && !(ok = wait_on(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kTimeoutTmemEmpty))) break;
+                    if (!(ok = wait_on(bar_full + 8 * stage, phase, abort_flag, kTimeoutFull))) break;
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + stage * S::kStageBytes);
                     const uint64_t a_desc = smem_descriptor(a_addr), a_lo_desc = smem_descriptor(a_addr + S::kABytes),
@@ -397,37 +273,43 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     }
     if (S::kFold && (warp == 1 || warp == 2)) {
         // ---------------- MMA issuers of the per-block modes: two threads ----------------
-        // Block g goes to accumulator buffer g % kAccBuffers (2 buffers of 256 columns, or 4 of 128) and is issued by thread g % 2.  One
-        // thread alone spends more time per block on its barrier tests and commits than the four MMAs run; with two, one thread's
-        // bookkeeping overlaps the other one's MMAs.
+        // Block kb of a tile goes to accumulator buffer kb % kAccBuffers (2 buffers of 256 columns, or 4 of 128: the drain warps' loop
+        // over the blocks is unrolled by the buffers, so every buffer has its own code there); block g of the CTA's sequence is issued
+        // by thread g % 2.  One thread alone spends more time per block on its barrier tests and commits than the four MMAs run; with
+        // two, one thread's bookkeeping overlaps the other one's MMAs.
         if (lane == 0) {
-            static_assert(!S::kFold || (kStages % 2 == 0 && kAccBuffers % 2 == 0), "two issuers alternate over even numbers of stages and buffers");
+            static_assert(!S::kFold || (kStages >= 2 && kAccBuffers % 2 == 0), "two issuers alternate over the stages and an even number of buffers");
             constexpr uint32_t idesc = instruction_descriptor(BN);
             const int me = warp - 1;
             const int total = ((tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x)) * kblocks;
-            int stage = me, acc = me;
-            uint32_t phase = 0, acc_phase = 0;
+            int stage = me % kStages;
+            uint32_t phase = 0;
+            int kb = me % kblocks, tile_ordinal = me / kblocks;  // position of block g in the CTA's sequence of tiles
             for (int g = me; g < total; g += 2) {
+                // uses of this buffer so far: per tile ceil((kblocks - acc) / kAccBuffers), plus those of this tile
+                const int acc = kb % kAccBuffers;
+                const int per_tile = acc < kblocks ? (kblocks - acc + kAccBuffers - 1) / kAccBuffers : 0;
+                const uint32_t acc_phase = uint32_t(tile_ordinal * per_tile + kb / kAccBuffers) & 1u;
                 const uint32_t d = tmem_base + acc * S::kAccColumns;
-                if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kTimeoutTmemEmpty)) break;
-                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, kTimeoutFull)) break;
+                if (!wait_on(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kTimeoutTmemEmpty)) break;
+                if (!wait_on(bar_full + 8 * stage, phase, abort_flag, kTimeoutFull)) break;
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(smem + stage * S::kStageBytes);
                 const uint64_t a_desc = smem_descriptor(a_addr), a_lo_desc = smem_descriptor(a_addr + S::kABytes),
                                b_desc = smem_descriptor(a_addr + S::kABytes * (S::kHilo ? 2 : 1));
 #pragma unroll
                 for (int j = 0; j < kStageK / kMmaK; ++j) {
-                    const uint32_t accumulate = (!kBiased && j == 0) ? 0u : 1u;
+                    const uint32_t accumulate = j == 0 ? 0u : 1u;  // every block starts a fresh sum
                     const uint64_t step = uint64_t(j * kMmaK >> 4);
                     mma_i8(d, a_desc + step, b_desc + step, idesc, accumulate);
                     if (S::kHilo) mma_i8(d + BN, a_lo_desc + step, b_desc + step, idesc, accumulate);
                 }
                 tc_commit(bar_empty + 8 * stage);
                 tc_commit(bar_acc_full + 8 * acc);
-                stage += 2;
+                stage += 2;  // at most one wrap per step (kStages >= 2)
                 if (stage >= kStages) { stage -= kStages; phase ^= 1u; }
-                acc += 2;
-                if (acc >= kAccBuffers) { acc -= kAccBuffers; acc_phase ^= 1u; }
+                kb += 2;
+                while (kb >= kblocks) { kb -= kblocks; ++tile_ordinal; }
             }
         }
     }
@@ -437,33 +319,34 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         // L2 (long, while the operand loads keep it busy) in front of every group of outputs; this warp puts them into shared memory
         // one tile ahead instead: as FP32 weight scale, bias (0 if none) and residual scale (1 if none) in the output type.
         if constexpr (!DUMP) {
-            const T* bias = static_cast<const T*>(p.bias);
             const T* rscale = static_cast<const T*>(p.rscale);
             int slot = 0, tile_count = 0;
             uint32_t phase = 0;
             bool ok = true;
             auto stage_params = [&](const TileCoord& c) -> bool {
                 if (!p.vector_io) return true;
-                // every epilogue warp is done with the previous tile's parameters
-                if (tile_count > 0 && !mbar_wait(bar_params_consumed, uint32_t(tile_count - 1) & 1u, abort_flag, kTimeoutParams)) return false;
+                // every drain warp is done with the previous tile's parameters
+                if (tile_count > 0 && !wait_on(bar_params_consumed, uint32_t(tile_count - 1) & 1u, abort_flag, kTimeoutParams)) return false;
+                const float* sb = p.sb[c.segment];
+                const T* bias = static_cast<const T*>(p.bias[c.segment]);
                 for (int i = lane; i < BN; i += 32) {
                     const int col = c.n0 + i;
                     const bool inside = col < p.n;
-                    param_sb[i] = !S::kWGroup && inside ? __ldg(p.sb + col) : 0.f;
+                    param_sb[i] = !S::kWGroup && inside ? __ldg(sb + col) : 0.f;
                     param_bias[i] = bias && inside ? bias[col] : round_one<T>(0.f);
-                    param_rscale[i] = rscale && inside ? rscale[col] : round_one<T>(1.f);
+                    param_rscale[i] = rscale && !p.window.span && inside ? rscale[col] : round_one<T>(1.f);
                 }
                 mbar_arrive(bar_params_written);
                 ++tile_count;
                 return true;
             };
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-                const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n);
+                const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n, p.seg_tiles);
                 if constexpr (S::kWGroup) {
-                    // the first two blocks' scales go first: the epilogue warps start on them right after the previous tile's write-out
+                    // the first two blocks' scales go first: the drain warps start on them right after the previous tile's write-out
                     const int params_after = (kblocks < 2 ? kblocks : 2) - 1;
                     for (int kb = 0; kb < kblocks && ok; ++kb) {
-                        if (!(ok = mbar_wait(bar_ring_empty + 8 * slot, phase ^ 1u, abort_flag, kTimeoutScales))) break;
+                        if (!(ok = wait_on(bar_ring_empty + 8 * slot, phase ^ 1u, abort_flag, kTimeoutScales))) break;
                         // the tile's BN scales of this block are contiguous in sb_blocks: one bulk copy, up to kScaleRing of them in flight
                         if (lane == 0) {
                             mbar_expect_tx(bar_ring_full + 8 * slot, BN * 4);
@@ -482,52 +365,34 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             }
         }
     }
-    } else if (warp >= 4 + kEpilogueWarps) {
-        // ---------------- re-arm (accumulators that start at the conversion bias) ----------------
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kSmallRegs));
-        if constexpr (kBiased) {
-            const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
-            const long long blocks = (long long)((tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x)) * kblocks;
-            int acc = 0;
-            uint32_t acc_phase = 0;
-            for (long long b = 0; b < blocks; ++b) {
-                if (!__all_sync(0xffffffffu, mbar_wait(bar_drained + 8 * acc, acc_phase, abort_flag, kTimeoutTmemEmpty))) break;
-                tc_fence_after();
-#pragma unroll
-                for (int column = 0; column < S::kAccColumns; column += 32) tmem_store_32(lane_addr + acc * S::kAccColumns + column, bias_run);
-                tmem_store_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
-                if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1u; }
-            }
-        }
     } else {
-        // ---------------- epilogue ----------------
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpilogueRegs));
-        const int quarter = warp & 3, half = (warp - 4) >> 2;
+        // ---------------- drain ----------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kDrainRegs));
+        const int quarter = warp & 3, part = (warp - kControlWarps) >> 2;  // lanes 32 quarter .. + 32, columns kEpi part .. + kEpi
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-        const T* bias = static_cast<const T*>(p.bias);
         const T* residual = static_cast<const T*>(p.residual);
         const T* rscale = static_cast<const T*>(p.rscale);
-        T* y = static_cast<T*>(p.y);
-        int acc = 0, slot = 0, store_buffer = 0;
+        const float* sa = p.sa + in_shift * (S::kBlockScales ? kblocks : 1);
+        int acc = 0, slot = 0;              // row / exact: the buffer of the tile being finished
         uint32_t acc_phase = 0, ring_phase = 0;
+        uint32_t buffer_phases = 0;         // per-block modes: bit b = phase of buffer b's next use
         bool ok = true;
-        const uint32_t my_stage = store_stage + (warp - 4) * S::kStoreBuffers * S::kStoreTile;
+        const int drain_warp = warp - kControlWarps;
+        const uint32_t my_stage = store_stage + drain_warp * S::kStoreTile;
         int tile_count = 0;  // tiles this CTA has finished: the phase of the parameter hand-over barriers
         float sa_ahead[2] = {0.f, 0.f};
         bool sa_ahead_valid = false;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-            const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n);
+            const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n, p.seg_tiles);
             const int row = c.m0 + quarter * 32 + lane;
             const bool row_ok = row < p.m;
-            const int col0 = c.n0 + half * kEpi;
-            const float row_scale = S::kBlockScales ? 1.f : (row_ok ? __ldg(p.sa + row) : 0.f);
+            const int col0 = c.n0 + part * kEpi;
+            const float row_scale = S::kBlockScales ? 1.f : (row_ok ? __ldg(sa + row) : 0.f);
+            T* y = static_cast<T*>(p.y[c.segment]) + out_shift * p.ld_y;
             // The tile's column parameters arrive in shared memory from warp 3; false when the CTA aborts.
             auto await_params = [&]() -> bool {
                 if (!p.vector_io) return true;
-                return __all_sync(0xffffffffu, mbar_wait(bar_params_written, uint32_t(tile_count) & 1u, abort_flag, kTimeoutParams));
+                return __all_sync(0xffffffffu, wait_on(bar_params_written, uint32_t(tile_count) & 1u, abort_flag, kTimeoutParams));
             };
             auto params_done = [&]() {
                 if (!p.vector_io) return;
@@ -536,27 +401,26 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                 ++tile_count;
             };
 
-            // y values of 32 columns starting at `col`: bias, residual, one rounding, store.  The accumulators of a tile live in registers,
-            // so this body is instantiated once per 32 columns of the thread: it is kept short (the tile epilogue runs once per tile and
-            // its instructions come from memory each time when the kernel outgrows the instruction cache).
+            // y values of 32 columns starting at `col` (chunk = index of the 32-column chunk among this thread's): bias, residual, one
+            // rounding, store.  The accumulators of a tile live in registers, so this body is instantiated once per 32 columns of the
+            // thread: it is kept short.
             auto emit = [&](const float* v, int col, int chunk) {
                 if (col >= p.n) return;
                 T* dst = y + int64_t(row) * p.ld_y + col;
-                const T* res = residual && row_ok ? residual + int64_t(row) * p.ld_residual + col : nullptr;
+                const T* res = residual && row_ok ? residual + (out_shift + row) * p.ld_residual + col : nullptr;
                 if (p.vector_io) {
                     // N is a multiple of 8 and every operand 16-byte aligned: eight outputs per step with 128-bit accesses; groups of eight
                     // are whole or absent at the right edge, rows past M are clipped by the TMA store (or skipped by the plain one)
                     const bool staged = p.tma_y != 0;
-                    const bool wide = S::kStoreBuffers == 2 && p.wide_store != 0, second = wide && (chunk & 1);
-                    const uint32_t stage_tile = wide ? my_stage : my_stage + store_buffer * S::kStoreTile;
+                    constexpr bool wide = S::kWide;
+                    const bool second = wide && (chunk & 1);
                     if (staged && !second) {
                         // the TMA store that last read this buffer must be done with it before the warp writes it again
-                        if (lane == 0) {
-                            if (wide) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                            else asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(S::kStoreBuffers - 1) : "memory");
-                        }
+                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                         __syncwarp();
                     }
+                    // residual scales of a row window with spans: per row, straight from memory
+                    const T* rs_row = rscale && p.window.span ? rscale + (out_shift + row) / p.window.span * p.window.scale_step : nullptr;
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
                         if (col + j >= p.n) break;
@@ -576,7 +440,8 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                         if (res) {
                             float res8[8], rs8[8];
                             load_eight_plain(res + j, res8);  // read before this thread overwrites it (y may be the residual)
-                            load_eight_plain(param_rscale + ct, rs8);
+                            if (rs_row) load_eight(rs_row + col + j, rs8, true);
+                            else load_eight_plain(param_rscale + ct, rs8);
 #pragma unroll
                             for (int e = 0; e < 8; ++e) out[e] = fmaf(out[e], rs8[e], res8[e]);
                         }
@@ -590,7 +455,7 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                             // (wide: piece 4 (chunk & 1) + j / 8 of a 128-byte row, 128-byte swizzle)
                             const uint32_t piece = wide ? (uint32_t(((chunk & 1) << 2) | (j >> 3)) ^ (uint32_t(lane) & 7u))
                                                         : (uint32_t(j >> 3) ^ ((uint32_t(lane) >> 1) & 3u));
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_tile + lane * (wide ? 128 : 64) + piece * 16), "r"(packed.x),
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_stage + lane * (wide ? 128 : 64) + piece * 16), "r"(packed.x),
                                          "r"(packed.y), "r"(packed.z), "r"(packed.w)
                                          : "memory");
                         } else if (row_ok) {
@@ -602,87 +467,93 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         __syncwarp();
                         if (lane == 0) {
-                            for (int d = 0; d < p.destinations; ++d)
-                                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&out_maps.map[d]),
-                                             "r"(second ? col - 32 : col), "r"(c.m0 + quarter * 32), "r"(stage_tile)
+                            // segments: map s is the output of weight s; else one map per destination of the same output
+                            const int first_map = p.destinations > 1 ? 0 : c.segment, maps = p.destinations > 1 ? p.destinations : 1;
+                            for (int d = 0; d < maps; ++d)
+                                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&out_maps.map[first_map + d]),
+                                             "r"(second ? col - 32 : col), "r"(c.m0 + quarter * 32), "r"(my_stage)
                                              : "memory");
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
-                        if (!wide && ++store_buffer == S::kStoreBuffers) store_buffer = 0;
                     }
                     return;
                 }
-                // Odd N or unaligned operands: one element at a time.  The values go through this thread's 64 bytes of a staging tile
+                // Odd N or unaligned operands: one element at a time.  The values go through this thread's 64 bytes of the staging tile
                 // (no TMA store is in flight in such a launch), 16 at a time, so that a short loop can index them.
+                const float* sb = p.sb[c.segment];
+                const T* bias = static_cast<const T*>(p.bias[c.segment]);
 #pragma unroll
-                for (int part = 0; part < 32; part += 16) {
-                    float* mine = store_stage_generic + ((warp - 4) * S::kStoreBuffers * S::kStoreTile + lane * 64) / 4;
+                for (int part16 = 0; part16 < 32; part16 += 16) {
+                    float* mine = store_stage_generic + (drain_warp * S::kStoreTile + lane * 64) / 4;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) mine[j] = v[part + j];
+                    for (int j = 0; j < 16; ++j) mine[j] = v[part16 + j];
 #pragma unroll 1
                     for (int j = 0; j < 16; ++j) {
-                        const int cj = col + part + j;
+                        const int cj = col + part16 + j;
                         if (row_ok && cj < p.n) {
-                            const float col_scale = S::kWGroup ? 1.f : __ldg(p.sb + cj);
+                            const float col_scale = S::kWGroup ? 1.f : __ldg(sb + cj);
                             float value = fmaf(mine[j] * row_scale, col_scale, bias ? as_float(bias[cj]) : 0.f);
-                            if (res) value = fmaf(value, rscale ? as_float(rscale[cj]) : 1.f, as_float(res[part + j]));
-                            dst[part + j] = round_one<T>(value);
+                            if (res) {
+                                const T* rs = rscale && p.window.span ? rscale + (out_shift + row) / p.window.span * p.window.scale_step : rscale;
+                                value = fmaf(value, rs ? as_float(rs[cj]) : 1.f, as_float(res[part16 + j]));
+                            }
+                            dst[part16 + j] = round_one<T>(value);
                         }
                     }
                 }
             };
 
             if constexpr (S::kFold) {
-                float accf[kEpi];
+                // FP32 accumulators of this thread's kEpi columns, as pairs for the two-wide FP32 instructions
+                float2 accf[kEpi / 2];
 #pragma unroll
-                for (int j = 0; j < kEpi; ++j) accf[j] = 0.f;
-                // activation block scales: two blocks ahead in registers
+                for (int j = 0; j < kEpi / 2; ++j) accf[j] = make_float2(0.f, 0.f);
+                // activation block scales of this thread's row: two blocks ahead in registers (rows past M read row 0's: never stored)
+                const float* sa_row = sa + int64_t(row_ok ? row : 0) * kblocks;
                 float sa_now = 0.f, sa_next = 0.f;
                 if constexpr (S::kBlockScales && !DUMP) {
                     if (sa_ahead_valid) {  // requested while the previous tile was being written out
                         sa_now = sa_ahead[0];
                         sa_next = sa_ahead[1];
                     } else {
-                        const float* sa_row = p.sa + int64_t(row_ok ? row : 0) * kblocks;
-                        sa_now = row_ok ? __ldg(sa_row) : 0.f;
-                        sa_next = row_ok && kblocks > 1 ? __ldg(sa_row + 1) : 0.f;
+                        sa_now = __ldg(sa_row);
+                        sa_next = kblocks > 1 ? __ldg(sa_row + 1) : 0.f;
                     }
                 }
-                for (int kb = 0; kb < kblocks; ++kb) {
-#ifdef WQ_TRACE
-                    const int stamp = (t / int(gridDim.x)) * kblocks + kb;
-                    const int tbase = (warp == 4 && lane == 0) ? 4096 : 1 << 30;
-#define WQ_ESTAMP(field) do { if (tbase == 4096) WQ_STAMP(4096, stamp, field); } while (0)
-#else
-#define WQ_ESTAMP(field) do {} while (0)
-#endif
-                    WQ_ESTAMP(0);
+                // One block of K: wait for its sums, bring them into registers in chunks of 16 columns (two sets of staging registers:
+                // chunks 0 and 1 are requested together, every later chunk into the set that has just been folded), hand the buffer back
+                // to the MMAs as soon as the last chunk has arrived -- half a drain before the folding ends -- and fold.  BUFFER is a
+                // compile-time constant: the loop over the blocks below is unrolled by the buffers.
+                auto drain_block = [&](auto buffer_tag, int kb) -> bool {
+                    constexpr int BUFFER = decltype(buffer_tag)::value;
                     float sa_after = 0.f;
                     if constexpr (S::kBlockScales && !DUMP) {
-                        if (row_ok && kb + 2 < kblocks) sa_after = __ldg(p.sa + int64_t(row) * kblocks + kb + 2);
+                        if (kb + 2 < kblocks) sa_after = __ldg(sa_row + kb + 2);
                     }
                     if constexpr (S::kWGroup) {
-                        if (!(ok = __all_sync(0xffffffffu, mbar_wait(bar_ring_full + 8 * slot, ring_phase, abort_flag, kTimeoutScales)))) break;
+                        if (!wait_on(bar_ring_full + 8 * slot, ring_phase, abort_flag, kTimeoutScales)) return false;
                     }
-                    if (!(ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, kTimeoutTmemFull)))) break;
-                    WQ_ESTAMP(1);
+                    if (!wait_on(bar_acc_full + 8 * BUFFER, (buffer_phases >> BUFFER) & 1u, abort_flag, kTimeoutTmemFull)) return false;
+                    buffer_phases ^= 1u << BUFFER;
                     tc_fence_after();
-                    const uint32_t taddr = tmem_base + lane_base + acc * S::kAccColumns + half * kEpi;
-                    const float* ring = scale_ring + slot * BN + half * kEpi;
-                    // Two staging buffers of 32 columns.  The buffer in tensor memory is handed back as soon as its last column has been
-                    // read (and re-armed), half a drain before the folding ends: the MMAs of the block after next start that much earlier.
-                    int hi[2][32], lo[2][32];
-                    constexpr int kChunks = kEpi / 32;
+                    const uint32_t taddr = tmem_base + lane_base + BUFFER * S::kAccColumns + part * kEpi;
+                    const float* ring = scale_ring + slot * BN + part * kEpi;
+                    constexpr int CH = Roles<PARTS>::kChunk < kEpi ? Roles<PARTS>::kChunk : kEpi, kChunks = kEpi / CH;
+                    int hi[2][CH], lo[2][S::kHilo ? CH : 1];
                     auto fetch = [&](int chunk) {
-                        tmem_load_32(taddr + chunk * 32, hi[chunk & 1]);
-                        if (S::kHilo) tmem_load_32(taddr + BN + chunk * 32, lo[chunk & 1]);
+                        if constexpr (CH == 32) {
+                            tmem_load_32(taddr + chunk * CH, hi[chunk & 1]);
+                            if constexpr (S::kHilo) tmem_load_32(taddr + BN + chunk * CH, lo[chunk & 1]);
+                        } else {
+                            tmem_load_16(taddr + chunk * CH, hi[chunk & 1]);
+                            if constexpr (S::kHilo) tmem_load_16(taddr + BN + chunk * CH, lo[chunk & 1]);
+                        }
                     };
                     auto release = [&]() {
-                        // every column of this warp's part of the buffer has been read: it goes back to the MMAs, through the re-arm warps
-                        // when the accumulators have to start at the conversion bias again
+                        // every column of this warp's part of the buffer is in registers: the buffer goes back to the MMAs
                         tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive((kBiased ? bar_drained : bar_acc_empty) + 8 * acc);
+                        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * BUFFER);
                     };
                     auto fold = [&](int chunk) {
                         const int* h = hi[chunk & 1];
@@ -690,64 +561,59 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                         if constexpr (DUMP) {
                             if (row_ok)
 #pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                    if (col0 + chunk * 32 + j < p.n) p.dump[(int64_t(kb) * p.m + row) * p.n + col0 + chunk * 32 + j] = h[j];
+                                for (int j = 0; j < CH; ++j)
+                                    if (col0 + chunk * CH + j < p.n) p.dump[(int64_t(kb) * p.m + row) * p.n + col0 + chunk * CH + j] = h[j];
                         } else {
-                            // three passes over the chunk, each of 32 independent instructions, converting in place: the dependent
-                            // add -> subtract -> multiply-add of one element are never issued back to back
-                            float v[32];
+                            const float2 sa2 = make_float2(sa_now, sa_now);
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] = __int_as_float(FOLD == kFoldAdd ? h[j] + kBiasBits : h[j]);
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] -= kBiasValue;
-                            if constexpr (MODE == kExactG) {
-                                float w[32];
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) w[j] = __int_as_float(FOLD == kFoldAdd ? l[j] + kBiasBits : l[j]);
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) w[j] -= kBiasValue;
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) v[j] = fmaf(w[j], 1.f / 254.f, v[j]);
-                            }
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                float* a = &accf[chunk * 32 + j];
+                            for (int j = 0; j < CH / 2; ++j) {
+                                float2 v = make_float2(float(h[2 * j]), float(h[2 * j + 1]));
+                                float2& a = accf[chunk * (CH / 2) + j];
                                 if constexpr (MODE == kBlock) {
-                                    *a = fmaf(v[j], sa_now, *a);
-                                } else if constexpr (MODE == kBlockG) {
-                                    *a = fmaf(v[j], sa_now * ring[chunk * 32 + j], *a);
+                                    a = __ffma2_rn(v, sa2, a);
                                 } else {
-                                    *a = fmaf(v[j], ring[chunk * 32 + j], *a);
+                                    const float2 w = *reinterpret_cast<const float2*>(ring + chunk * CH + 2 * j);
+                                    if constexpr (MODE == kBlockG) {
+                                        a = __ffma2_rn(v, __fmul2_rn(sa2, w), a);
+                                    } else {
+                                        const float2 low = make_float2(float(l[2 * j]), float(l[2 * j + 1]));
+                                        v = __ffma2_rn(low, make_float2(1.f / 254.f, 1.f / 254.f), v);
+                                        a = __ffma2_rn(v, w, a);
+                                    }
                                 }
                             }
                         }
                     };
-                    static_assert(kChunks >= 2 && kChunks % 2 == 0, "the drain works on pairs of 32-column chunks");
                     fetch(0);
-                    fetch(1);
+                    if (kChunks > 1) fetch(1);
                     tmem_load_wait();
-                    WQ_ESTAMP(2);
-                    if (kChunks == 2) release();
+                    if (kChunks <= 2) release();
 #pragma unroll
                     for (int chunk = 0; chunk < kChunks; ++chunk) {
                         fold(chunk);
                         if (chunk + 2 < kChunks) {
-                            fetch(chunk + 2);  // into the staging buffer just folded
-                            if (chunk & 1) {   // chunks chunk + 1 and chunk + 2 are in flight: complete the pair
-                                tmem_load_wait();
-                                if (chunk + 2 == kChunks - 1) { WQ_ESTAMP(3); release(); WQ_ESTAMP(4); }
+                            fetch(chunk + 2);  // into the set just folded
+                            if (chunk + 2 == kChunks - 1) {
+                                tmem_load_wait();  // every column is in registers
+                                release();
                             }
                         }
                     }
                     if constexpr (S::kWGroup) {
                         __syncwarp();
                         if (lane == 0) mbar_arrive(bar_ring_empty + 8 * slot);
+                        if (++slot == kScaleRing) { slot = 0; ring_phase ^= 1u; }
                     }
-                    WQ_ESTAMP(5);
-                    if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1u; }
-                    if (S::kWGroup && ++slot == kScaleRing) { slot = 0; ring_phase ^= 1u; }
                     sa_now = sa_next;
                     sa_next = sa_after;
+                    return true;
+                };
+                // block kb of the tile uses buffer kb % kAccBuffers (the MMA issuers follow the same rule)
+                for (int kb = 0; kb < kblocks && ok; kb += kAccBuffers) {
+                    ok = drain_block(std::integral_constant<int, 0>(), kb);
+                    if constexpr (kAccBuffers > 1) if (ok && kb + 1 < kblocks) ok = drain_block(std::integral_constant<int, 1>(), kb + 1);
+                    if constexpr (kAccBuffers > 2) if (ok && kb + 2 < kblocks) ok = drain_block(std::integral_constant<int, 2>(), kb + 2);
+                    if constexpr (kAccBuffers > 3) if (ok && kb + 3 < kblocks) ok = drain_block(std::integral_constant<int, 3>(), kb + 3);
                 }
                 if (!ok) break;
                 if constexpr (S::kBlockScales && !DUMP) {
@@ -755,28 +621,30 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                     const int t_next = t + int(gridDim.x);
                     sa_ahead_valid = t_next < tiles;
                     if (sa_ahead_valid) {
-                        const int row_next = tile_origin<BN>(t_next, p.tiles_m, p.tiles_n).m0 + quarter * 32 + lane;
-                        const float* sa_row = p.sa + int64_t(row_next < p.m ? row_next : 0) * kblocks;
-                        sa_ahead[0] = row_next < p.m ? __ldg(sa_row) : 0.f;
-                        sa_ahead[1] = row_next < p.m && kblocks > 1 ? __ldg(sa_row + 1) : 0.f;
+                        const int row_next = tile_origin<BN>(t_next, p.tiles_m, p.tiles_n, p.seg_tiles).m0 + quarter * 32 + lane;
+                        const float* next_row = sa + int64_t(row_next < p.m ? row_next : 0) * kblocks;
+                        sa_ahead[0] = __ldg(next_row);
+                        sa_ahead[1] = kblocks > 1 ? __ldg(next_row + 1) : 0.f;
                     }
                 }
-#ifdef WQ_TRACE
-                if (warp == 4 && lane == 0) WQ_STAMP(4096, (t / int(gridDim.x)) * kblocks + kblocks - 1, 6);
-#endif
                 if constexpr (!DUMP) {
                     if (!(ok = await_params())) break;
 #pragma unroll
-                    for (int chunk = 0; chunk < kEpi / 32; ++chunk) emit(&accf[chunk * 32], col0 + chunk * 32, chunk);
+                    for (int chunk = 0; chunk < kEpi / 32; ++chunk) {
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            v[2 * j] = accf[chunk * 16 + j].x;
+                            v[2 * j + 1] = accf[chunk * 16 + j].y;
+                        }
+                        emit(v, col0 + chunk * 32, chunk);
+                    }
                     params_done();
                 }
-#ifdef WQ_TRACE
-                if (warp == 4 && lane == 0) WQ_STAMP(4096, (t / int(gridDim.x)) * kblocks + kblocks - 1, 7);
-#endif
             } else {
-                if (!(ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, kTimeoutTmemFull)))) break;
+                if (!(ok = __all_sync(0xffffffffu, wait_on(bar_acc_full + 8 * acc, acc_phase, abort_flag, kTimeoutTmemFull)))) break;
                 tc_fence_after();
-                const uint32_t taddr = tmem_base + lane_base + acc * S::kAccColumns + half * kEpi;
+                const uint32_t taddr = tmem_base + lane_base + acc * S::kAccColumns + part * kEpi;
                 if (!(ok = await_params())) break;
 #pragma unroll 1
                 for (int chunk = 0; chunk < kEpi / 32; ++chunk) {
@@ -802,79 +670,13 @@ gemm_i8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                 if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1u; }
             }
         }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staged outputs
     }
 
     // common exit: every role falls through to here, aborting or not
-    if (warp >= 4 && warp < 4 + kEpilogueWarps && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staged outputs
     tc_fence_before();
     __syncthreads();
     if (warp == 2) {
-        tc_fence_after();
-        tmem_dealloc(tmem_base, kTmemColumns);
-    }
-}
-
-// Issue-rate probe of the tensor pipe: one CTA per SM issues `iters` groups of four M128 N256 MMAs on resident shared-memory
-// operands (no loads, no epilogue), alternating the two accumulator buffers.  KIND 0: kind::i8 (K = 32), 1: kind::f16 with BF16 (K = 16).
-template <int KIND>
-__global__ void __launch_bounds__(128, 1) mma_peak_probe(int iters, long long* cycles, long long* nanoseconds) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ uint32_t tmem_slot;
-    __shared__ uint64_t bar;
-    __shared__ int abort_word;
-    // operands: zeros (the quietest data) or pseudo-random bytes (iters < 0): the tensor pipe's power, and with it the clock, depends on them
-    const bool noisy = iters < 0;
-    if (noisy) iters = -iters;
-    for (int i = threadIdx.x; i < (kBM + 256) * kStageK / 16; i += blockDim.x) {
-        uint32_t h = (i * 4 + blockIdx.x * 7919u) * 2654435761u;
-        const uint4 v = make_uint4(h, h * 2246822519u, h * 3266489917u, h * 668265263u);
-        reinterpret_cast<uint4*>(smem)[i] = noisy ? v : make_uint4(0u, 0u, 0u, 0u);
-    }
-    if (threadIdx.x == 0) {
-        abort_word = 0;
-        mbar_init(smem_u32(&bar), 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the zeroes above are read by the tensor cores
-    if (threadIdx.x < 32) tmem_alloc(smem_u32(&tmem_slot), kTmemColumns);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = tmem_slot;
-    if (threadIdx.x == 0) {
-        // KIND 1: F32 accumulator (1 << 4), BF16 A and B (1 << 7, 1 << 10)
-        constexpr uint32_t idesc = KIND == 0 ? instruction_descriptor(256)
-                                             : ((1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(256 >> 3) << 17) | (uint32_t(kBM >> 4) << 24));
-        const uint64_t a_desc = smem_descriptor(smem_u32(smem)), b_desc = smem_descriptor(smem_u32(smem) + kBM * kStageK);
-        long long t0 = clock64(), g0;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g0));
-        for (int i = 0; i < iters; ++i) {
-            const uint32_t d = tmem_base + (i & 1) * 256;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (KIND == 0) {
-                    mma_i8(d, a_desc + 2 * j, b_desc + 2 * j, idesc, 1u);
-                } else {
-                    asm volatile(
-                        "{\n\t.reg .pred p;\n\t"
-                        "setp.ne.b32 p, %4, 0;\n\t"
-                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d),
-                        "l"(a_desc + 2 * j), "l"(b_desc + 2 * j), "r"(idesc), "r"(1u)
-                        : "memory");
-                }
-            }
-        }
-        tc_commit(smem_u32(&bar));
-        mbar_wait(smem_u32(&bar), 0, &abort_word, kTimeoutTmemFull);
-        long long t1 = clock64(), g1;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
-        cycles[blockIdx.x] = t1 - t0;
-        nanoseconds[blockIdx.x] = g1 - g0;
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (threadIdx.x < 32) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemColumns);
     }
@@ -896,7 +698,7 @@ static EncodeTiled encode_tiled() {
 }
 
 // (rows, k) row-major INT8 matrix -> tensor map with boxes of `box_rows` rows x 128 bytes, 128-byte swizzle, zero fill outside.
-static bool make_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
+static bool make_map(CUtensorMap* map, const void* base, int64_t rows, int k, int box_rows) {
     EncodeTiled encode = encode_tiled();
     if (!encode) return false;
     const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(rows)};
@@ -961,12 +763,22 @@ struct GemmArgs {
     void* const* ys = nullptr;  // `count` destinations of the output (host array of device pointers); y when null
     int count = 1;
     int64_t ld_y = 0, ld_residual = 0;  // 0: contiguous (N)
+    // several weights of one input (n = output channels of each): per-segment weight, scales, bias and output
+    int segments = 1;
+    const int8_t* const* seg_b = nullptr;
+    const float* const* seg_sb = nullptr;
+    const void* const* seg_bias = nullptr;
+    void* const* seg_y = nullptr;
+    RowWindow window = {nullptr, 0, 0, 0, 0, 0, 0};
 };
 
-template <class T, int MODE, int BN, int FOLD, bool DUMP>
+// Rows a tensor map of a row window may address: the window's position is only known on the GPU.
+constexpr int64_t kUnboundedRows = int64_t(1) << 30;
+
+template <class T, int MODE, int BN, bool WIDE, bool DUMP, int PARTS>
 static int launch(const GemmArgs& g, cudaStream_t stream) {
-    using S = Shape<MODE, BN>;
-    auto kernel = gemm_i8_tc<T, MODE, BN, FOLD, DUMP>;
+    using S = Shape<MODE, BN, WIDE, PARTS>;
+    auto kernel = gemm_i8_tc<T, MODE, BN, WIDE, DUMP, PARTS>;
     static bool configured[64] = {};  // the attribute belongs to a device's copy of the kernel
     int device = 0;
     cudaGetDevice(&device);
@@ -975,28 +787,46 @@ static int launch(const GemmArgs& g, cudaStream_t stream) {
         if (e != cudaSuccess) return int(e);
         if (device >= 0 && device < 64) configured[device] = true;
     }
-    if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15) || (g.a_lo && (reinterpret_cast<uintptr_t>(g.a_lo) & 15)))
-        return -2;
-    CUtensorMap map_a, map_a_lo, map_b;
+    if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (g.a_lo && (reinterpret_cast<uintptr_t>(g.a_lo) & 15))) return -2;
+    const bool windowed = g.window.counter != nullptr;
+    InputMaps in_maps;
+    WeightMaps w_maps;
     OutputMaps out_maps;
-    if (!make_map(&map_a, g.a, g.m, g.k, kBM) || !make_map(&map_b, g.b, g.n, g.k, BN)) return int(cudaErrorNotSupported);
-    if (S::kHilo) {
-        if (!make_map(&map_a_lo, g.a_lo, g.m, g.k, kBM)) return int(cudaErrorNotSupported);
-    } else {
-        map_a_lo = map_a;
-    }
     GemmParams p{};
-    p.sa = g.sa; p.sb = g.sb; p.bias = g.bias; p.residual = g.residual; p.rscale = g.rscale; p.dump = g.dump;
-    p.y = g.ys ? g.ys[0] : g.y;
+    const int64_t a_rows = windowed ? kUnboundedRows : g.m;
+    p.tail_rows = windowed ? g.m % kBM : 0;
+    if (!make_map(&in_maps.a, g.a, a_rows, g.k, kBM)) return int(cudaErrorNotSupported);
+    in_maps.a_lo = in_maps.a_tail = in_maps.a_lo_tail = in_maps.a;
+    if (S::kHilo && !make_map(&in_maps.a_lo, g.a_lo, a_rows, g.k, kBM)) return int(cudaErrorNotSupported);
+    if (p.tail_rows) {
+        if (!make_map(&in_maps.a_tail, g.a, a_rows, g.k, p.tail_rows)) return int(cudaErrorNotSupported);
+        if (S::kHilo && !make_map(&in_maps.a_lo_tail, g.a_lo, a_rows, g.k, p.tail_rows)) return int(cudaErrorNotSupported);
+    }
+    uintptr_t bases = reinterpret_cast<uintptr_t>(g.residual) | reinterpret_cast<uintptr_t>(g.rscale);
+    for (int s = 0; s < kMaxSegments; ++s) {
+        const bool used = s < g.segments;
+        const int8_t* b = !used ? nullptr : g.seg_b ? g.seg_b[s] : g.b;
+        p.sb[s] = !used ? nullptr : g.seg_sb ? g.seg_sb[s] : g.sb;
+        p.bias[s] = !used ? nullptr : g.seg_bias ? g.seg_bias[s] : g.bias;
+        p.y[s] = !used ? nullptr : g.seg_y ? g.seg_y[s] : (g.ys ? g.ys[0] : g.y);
+        if (used) {
+            if (reinterpret_cast<uintptr_t>(b) & 15) return -2;
+            if (!make_map(&w_maps.map[s], b, g.n, g.k, BN)) return int(cudaErrorNotSupported);
+            bases |= reinterpret_cast<uintptr_t>(p.y[s]) | reinterpret_cast<uintptr_t>(p.bias[s]) | (S::kWGroup ? 0 : reinterpret_cast<uintptr_t>(p.sb[s]));
+        } else {
+            w_maps.map[s] = w_maps.map[0];
+        }
+    }
+    p.sa = g.sa; p.residual = g.residual; p.rscale = g.rscale; p.dump = g.dump;
     p.ld_y = g.ld_y ? g.ld_y : g.n;
     p.ld_residual = g.ld_residual ? g.ld_residual : g.n;
     p.destinations = g.ys ? g.count : 1;
-    if (p.destinations < 1 || p.destinations > kMaxDestinations) return -2;
+    if (p.destinations < 1 || p.destinations > kMaxDestinations || (p.destinations > 1 && g.segments > 1)) return -2;
     p.m = g.m; p.n = g.n; p.k = g.k;
     p.tiles_m = (g.m + kBM - 1) / kBM;
-    p.tiles_n = (g.n + BN - 1) / BN;
-    uintptr_t bases = reinterpret_cast<uintptr_t>(p.y) | reinterpret_cast<uintptr_t>(g.residual) | reinterpret_cast<uintptr_t>(g.bias) |
-                            reinterpret_cast<uintptr_t>(g.rscale) | (S::kWGroup ? 0 : reinterpret_cast<uintptr_t>(g.sb));
+    p.seg_tiles = (g.n + BN - 1) / BN;
+    p.tiles_n = p.seg_tiles * g.segments;
+    p.window = g.window;
     if (S::kWGroup) {
         if (!g.scale_scratch || (reinterpret_cast<uintptr_t>(g.scale_scratch) & 15)) return -2;
         const int kblocks = (g.k + kStageK - 1) / kStageK;
@@ -1006,36 +836,57 @@ static int launch(const GemmArgs& g, cudaStream_t stream) {
         regroup_weight_scales<<<int((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184), 256, 0, stream>>>(g.sb, g.scale_scratch, g.n, kblocks, p.n_pad);
     }
     for (int d = 1; d < p.destinations; ++d) bases |= reinterpret_cast<uintptr_t>(g.ys[d]);
-    p.vector_io = g.n % 8 == 0 && p.ld_y % 8 == 0 && p.ld_residual % 8 == 0 && (bases & 15) == 0;
-    p.tma_y = !DUMP && p.vector_io;
-    p.wide_store = S::kStoreBuffers == 2 && p.destinations > 1;
+    p.vector_io = g.n % 8 == 0 && p.ld_y % 8 == 0 && p.ld_residual % 8 == 0 && (bases & 15) == 0 &&
+                  (!g.window.span || g.window.scale_step % 8 == 0);
+    // a row window's outputs leave through plain, row-predicated stores: where they go is only known on the GPU
+    p.tma_y = !DUMP && p.vector_io && !windowed;
+    const bool wide = S::kWide;
+    const int maps = p.destinations > 1 ? p.destinations : g.segments;
     for (int d = 0; d < kMaxDestinations; ++d) {
-        if (p.tma_y && d < p.destinations)
-            p.tma_y = make_output_map(&out_maps.map[d], d == 0 ? p.y : g.ys[d], g.m, g.n, p.ld_y, std::is_same<T, bf16>::value, p.wide_store != 0);
+        if (p.tma_y && d < maps)
+            p.tma_y = make_output_map(&out_maps.map[d], p.destinations > 1 ? (d == 0 ? p.y[0] : g.ys[d]) : p.y[d], g.m, g.n, p.ld_y,
+                                      std::is_same<T, bf16>::value, wide);
         else
-            out_maps.map[d] = map_a;
+            out_maps.map[d] = in_maps.a;
     }
     if (p.destinations > 1 && !p.tma_y) return -2;  // several destinations are only written by the TMA stores
     const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
     const int sms = g.sms > 0 ? g.sms : 148;
     const int grid = int(tiles < sms ? tiles : sms);
-    kernel<<<grid, kThreads, S::kSmemBytes, stream>>>(map_a, map_a_lo, map_b, out_maps, p);
+    kernel<<<grid, Roles<PARTS>::kThreads, S::kSmemBytes, stream>>>(in_maps, w_maps, out_maps, p);
     return int(cudaGetLastError());
 }
 
+template <class T, int MODE, int BN, int PARTS = 4> static int launch_width(const GemmArgs& g, cudaStream_t stream) {
+    // several destinations: staging tiles with 128-byte rows, one operand stage less
+    if (g.ys && g.count > 1) return launch<T, MODE, BN, true, false, PARTS>(g, stream);
+    return launch<T, MODE, BN, false, false, PARTS>(g, stream);
+}
+
+// Variant numbers keep the reference's meaning of the MODE (row 0 / 2 / 6, exact 1 / 7, block 10 / 11, block+g 12 / 13, exact+g 14);
+// the tile shapes are this library's own: 256 output channels per tile, or 128 for variants 13, 15, 16.  Variants 20 and 22 are 10 and 12
+// with eight drain warps of 128 columns instead of sixteen of 64: fewer instructions per output, fewer warps to hide latencies with.
 template <class T> static int dispatch(const GemmArgs& g, int variant, cudaStream_t stream) {
     switch (variant) {
-        case 0: case 2: case 6: return launch<T, kRow, 256, kFoldAdd, false>(g, stream);
-        case 1: case 7: return launch<T, kExact, 256, kFoldAdd, false>(g, stream);
-        case 10: return launch<T, kBlock, 256, kFoldBiased, false>(g, stream);
-        case 11: return launch<T, kBlock, 256, kFoldAdd, false>(g, stream);
-        case 12: return launch<T, kBlockG, 256, kFoldBiased, false>(g, stream);
-        case 13: return launch<T, kBlockG, 256, kFoldAdd, false>(g, stream);
-        case 14: return launch<T, kExactG, 128, kFoldBiased, false>(g, stream);
-        case 15: return launch<T, kBlock, 128, kFoldBiased, false>(g, stream);  // tiles of 128 columns: four accumulator buffers
-        case 16: return launch<T, kBlock, 128, kFoldAdd, false>(g, stream);
+        case 0: case 2: case 6: return launch_width<T, kRow, 256>(g, stream);
+        case 1: case 7: return launch_width<T, kExact, 256>(g, stream);
+        case 10: case 11: return launch_width<T, kBlock, 256>(g, stream);
+        case 12: return launch_width<T, kBlockG, 256>(g, stream);
+        case 13: return launch_width<T, kBlockG, 128>(g, stream);
+        case 14: return launch_width<T, kExactG, 128>(g, stream);
+        case 15: case 16: return launch_width<T, kBlock, 128>(g, stream);  // tiles of 128 columns: four accumulator buffers
+        case 20: return launch_width<T, kBlock, 256, 2>(g, stream);
+        case 22: return launch_width<T, kBlockG, 256, 2>(g, stream);
     }
     return -3;
+}
+
+static int gemm_entry(GemmArgs& g, int dtype, int variant, cudaStream_t stream) {
+    if ((variant == 1 || variant == 7 || variant == 14) != (g.a_lo != nullptr)) return -2;
+    if (g.k <= 0 || g.k % 16) return -2;
+    if (dtype == 0) return dispatch<__half>(g, variant, stream);
+    if (dtype == 1) return dispatch<bf16>(g, variant, stream);
+    return -1;
 }
 
 }  // namespace wq
@@ -1046,12 +897,22 @@ WQ_API int wq8_gemm(const int8_t* a, const int8_t* a_lo, const float* sa, const 
                     const void* rscale, void* y, int m, int n, int k, int dtype, int variant, int sms, int /*split*/, int* workspace,
                     int* /*counters*/, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
-    if ((variant == 1 || variant == 7 || variant == 14) != (a_lo != nullptr)) return -2;
-    if (k <= 0 || k % 16) return -2;
-    const GemmArgs g{reinterpret_cast<float*>(workspace), a, a_lo, sa, b, sb, bias, residual, rscale, y, nullptr, m, n, k, sms};
-    if (dtype == 0) return dispatch<__half>(g, variant, stream);
-    if (dtype == 1) return dispatch<bf16>(g, variant, stream);
-    return -1;
+    GemmArgs g{reinterpret_cast<float*>(workspace), a, a_lo, sa, b, sb, bias, residual, rscale, y, nullptr, m, n, k, sms};
+    return gemm_entry(g, dtype, variant, stream);
+}
+
+// wq8_gemm on a window of rows whose position is read on the GPU when the kernel runs: the output rows (and those of the residual) start
+// at first + counter[0] * step of y; the input rows (A, A_lo and their scales) at in_first + counter[0] * in_step when either is
+// non-zero; span > 0: rscale holds scale_step values per span of output rows.
+WQ_API int wq8_gemm_at(const int8_t* a, const int8_t* a_lo, const float* sa, const int8_t* b, const float* sb, const void* bias, const void* residual,
+                       const void* rscale, void* y, int m, int n, int k, int dtype, int variant, int sms, int /*split*/, int* workspace,
+                       int* /*counters*/, const long long* counter, long long first, long long step, long long span, long long scale_step,
+                       long long in_first, long long in_step, cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (span < 0) return -2;
+    GemmArgs g{reinterpret_cast<float*>(workspace), a, a_lo, sa, b, sb, bias, residual, rscale, y, nullptr, m, n, k, sms};
+    g.window = {counter, first, step, counter ? span : 0, scale_step, in_first, in_step};
+    return gemm_entry(g, dtype, variant, stream);
 }
 
 // wq8_gemm whose output goes to `count` destinations at once (ys: host array of device pointers to the first element of an (M, N)
@@ -1064,81 +925,73 @@ WQ_API int wq8_gemm_multi(const int8_t* a, const int8_t* a_lo, const float* sa, 
     if (!ys || count < 1 || count > kMaxDestinations || ld_y < n || (residual && ld_residual < n)) return -2;
     for (int d = 0; d < count; ++d)
         if (!ys[d]) return -2;
-    if ((variant == 1 || variant == 7 || variant == 14) != (a_lo != nullptr)) return -2;
-    if (k <= 0 || k % 16) return -2;
     GemmArgs g{reinterpret_cast<float*>(workspace), a, a_lo, sa, b, sb, bias, residual, rscale, ys[0], nullptr, m, n, k, sms};
     g.ys = ys;
     g.count = count;
     g.ld_y = ld_y;
     g.ld_residual = residual ? ld_residual : 0;
-    if (dtype == 0) return dispatch<__half>(g, variant, stream);
-    if (dtype == 1) return dispatch<bf16>(g, variant, stream);
-    return -1;
+    return gemm_entry(g, dtype, variant, stream);
 }
 
 // Whole tiles only: no partial sums, no counters.  The variants with group-scaled weights regroup the weight scales by block of K
 // into the workspace.
 WQ_API void wq8_gemm_workspace(int, int n, int k, int variant, int, int, int64_t* sizes) {
     sizes[0] = sizes[1] = 0;
-    if (variant >= 12 && variant <= 14 && n > 0 && k > 0) sizes[0] = int64_t((k + kStageK - 1) / kStageK) * padded_n(n) * 4;
+    if (((variant >= 12 && variant <= 14) || variant == 22) && n > 0 && k > 0) sizes[0] = int64_t((k + kStageK - 1) / kStageK) * padded_n(n) * 4;
 }
 
 WQ_API int wq8_gemm_select(int, int, int, int hilo, int) { return hilo ? 1 : 0; }
 
-// One launch per weight: the quantized input stays in L2 between them (a band of 2048 rows of codes is 10 MB), the values are those of
-// wq8_gemm on each weight.  Per-channel weight scales only, as in the reference.
+// `count` (1 to 4) linears of one input in ONE launch: the persistent tile schedule walks count x ceil(rows / tile) column tiles per row
+// band, each tile taking its weight, scales, bias and output from its segment, so the quantized input is read once for all of them.
+// Per-channel weight scales only, no residual, as in the reference.
 WQ_API int wq8_gemm_segments(const int8_t* a, const int8_t* a_lo, const float* sa, const int8_t* const* bs, const float* const* sbs,
-                             const void* const* biases, void* const* ys, int count, int rows, int m, int k, int dtype, int variant, int sms, int split,
-                             int* workspace, int* counters, cudaStream_t stream) {
-    if (count < 1 || count > 4 || rows <= 0 || rows % 8 || !bs || !sbs || !ys) return -4;
-    if (variant >= 12 && variant <= 14) return -4;
+                             const void* const* biases, void* const* ys, int count, int rows, int m, int k, int dtype, int variant, int sms, int /*split*/,
+                             int* workspace, int* /*counters*/, cudaStream_t stream) {
+    if (count < 1 || count > kMaxSegments || rows <= 0 || rows % 8 || !bs || !sbs || !ys) return -4;
+    if ((variant >= 12 && variant <= 14) || variant == 22) return -4;
     for (int s = 0; s < count; ++s)
         if (!bs[s] || !sbs[s] || !ys[s]) return -4;
-    for (int s = 0; s < count; ++s) {
-        const int code = wq8_gemm(a, a_lo, sa, bs[s], sbs[s], biases ? biases[s] : nullptr, nullptr, nullptr, ys[s], m, rows, k, dtype, variant, sms, split,
-                                  workspace, counters, stream);
-        if (code) return code;
-    }
-    return 0;
+    if (m <= 0) return 0;
+    const void* no_bias[kMaxSegments] = {nullptr, nullptr, nullptr, nullptr};
+    GemmArgs g{reinterpret_cast<float*>(workspace), a, a_lo, sa, bs[0], sbs[0], nullptr, nullptr, nullptr, ys[0], nullptr, m, rows, k, sms};
+    g.segments = count;
+    g.seg_b = bs;
+    g.seg_sb = sbs;
+    g.seg_bias = biases ? biases : no_bias;
+    g.seg_y = ys;
+    return gemm_entry(g, dtype, variant, stream);
 }
 
 WQ_API int wq8_debug_block_sums(const int8_t* a, const int8_t* b, int32_t* sums, int m, int n, int k, int sms, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (k <= 0 || k % 16) return -2;
     const GemmArgs g{nullptr, a, nullptr, nullptr, b, nullptr, nullptr, nullptr, nullptr, nullptr, sums, m, n, k, sms};
-    return launch<bf16, kBlock, 256, kFoldAdd, true>(g, stream);
+    return launch<bf16, kBlock, 256, false, true, 4>(g, stream);
 }
 
-// results[0] = tera-operations per second of the whole GPU, results[1] = SM clock in MHz during the probe, results[2] = clocks per MMA group.
-WQ_API int wq8_debug_mma_peak(int kind, int iters, int sms, double* results) {
-    if (iters == 0 || sms <= 0 || sms > 1024 || (kind != 0 && kind != 1)) return -2;
-    long long* buffers = nullptr;
-    if (cudaMalloc(&buffers, sizeof(long long) * 2 * sms) != cudaSuccess) return int(cudaGetLastError());
-    const int smem_bytes = (kBM + 256) * kStageK + 1024;
-    auto kernel = kind == 0 ? mma_peak_probe<0> : mma_peak_probe<1>;
-    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    for (int round = 0; round < 2; ++round) kernel<<<sms, 128, smem_bytes>>>(iters, buffers, buffers + sms);
-    int code = int(cudaDeviceSynchronize());
-    long long host[2048];
-    if (!code) code = int(cudaMemcpy(host, buffers, sizeof(long long) * 2 * sms, cudaMemcpyDeviceToHost));
-    cudaFree(buffers);
-    if (code) return code;
-    double cycles = 0, ns = 0;
-    for (int i = 0; i < sms; ++i) { cycles += double(host[i]); ns += double(host[sms + i]); }
-    cycles /= sms; ns /= sms;
-    const double ops = 2.0 * kBM * 256 * (kind == 0 ? 32 : 16) * 4.0 * (iters < 0 ? -iters : iters) * sms;
-    results[0] = ops / (ns * 1e-9) / 1e12;
-    results[1] = cycles / ns * 1e3;
-    results[2] = cycles / (iters < 0 ? -iters : iters);
-    return 0;
+// A bounded wait on a barrier that nothing ever completes, with a limit of `clocks`: the kernel must come back, leave `code` in the
+// status word and the device usable.  What the tests use to see the give-up path of every wait in this library work, without a fault.
+namespace wq {
+__global__ void bounded_wait_probe(long long clocks, int code, int* returned) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_word;
+    if (threadIdx.x == 0) {
+        abort_word = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const bool completed = mbar_wait(smem_u32(&bar), 0, &abort_word, code, &g_status, clocks);
+    if (threadIdx.x == 0) *returned = completed ? 1 : 2;
 }
+}  // namespace wq
 
-#ifdef WQ_TRACE
-WQ_API int wq8_debug_trace(long long* host_out) {
-    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    return int(cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 8192));
+WQ_API int wq8_debug_wait_probe(long long clocks, int code, int* returned, cudaStream_t stream) {
+    if (clocks <= 0 || clocks > 2000000000ll || !returned) return -2;
+    bounded_wait_probe<<<1, 64, 0, stream>>>(clocks, code, returned);
+    return int(cudaGetLastError());
 }
-#endif
 
 WQ_API int wq8_debug_status() {
     int code = 0;

@@ -6,6 +6,13 @@
 
 namespace wq {
 
+// Row window of the *_at entry points: the input rows start at row first + counter[0] * step of x, the counter being read on the GPU
+// when the kernel runs (a CUDA graph replays the launch while its loop counter advances).  No counter: row 0.
+struct RowShift { const long long* counter; long long first, step; };
+template <class T> WQ_DEVICE const T* first_row(const T* x, int64_t ldx, const RowShift& shift) {
+    return shift.counter ? x + (shift.first + __ldg(shift.counter) * shift.step) * ldx : x;
+}
+
 // ---- one 256-element chunk -> two 128-element blocks (16 lanes each): absmax, scale, INT8 codes --------------------------
 template <int GROUP>
 WQ_DEVICE void store_chunk_as_blocks(const float* v, int lane, int64_t row, int base, int k, int kblocks, int8_t* __restrict__ q,
@@ -35,7 +42,8 @@ WQ_DEVICE void store_chunk_as_blocks(const float* v, int lane, int64_t row, int 
 // Blocks are independent when no row statistic is needed: a warp per 256-element chunk, persistent warps, two chunks in flight per warp.
 template <class T, int GROUP, int ACT>
 __global__ void __launch_bounds__(256) quantize_blocks_stream(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, int m,
-                                                              int k, int64_t ldx) {
+                                                              int k, int64_t ldx, RowShift shift) {
+    x = first_row(x, ldx, shift);
     const int lane = threadIdx.x & 31;
     const int chunks = (k + kChunk - 1) / kChunk, kblocks = (k + kBlockK - 1) / kBlockK;
     const int64_t items = int64_t(m) * chunks, warps = int64_t(gridDim.x) * 8, warp_id = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
@@ -70,11 +78,11 @@ __global__ void __launch_bounds__(256) quantize_blocks_stream(const T* __restric
 // Sum of squares: thread (warp w, lane l) accumulates fmaf(v, v, ss) over chunks w, w + 8, ... in order; then the ordered CTA sum.
 template <class T, int GROUP, int CPW>
 __global__ void __launch_bounds__(kRowThreads) quantize_blocks_rms(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, int m, int k,
-                                                                   int64_t ldx, const T* __restrict__ act_weight, float eps) {
+                                                                   int64_t ldx, const T* __restrict__ act_weight, float eps, RowShift shift) {
     __shared__ float slots[8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t row = blockIdx.x;
-    const T* src = x + row * ldx;
+    const T* src = first_row(x, ldx, shift) + row * ldx;
     const int kblocks = (k + kBlockK - 1) / kBlockK;
     float ss = 0.f;
     if constexpr (CPW > 0) {
@@ -143,11 +151,12 @@ template <bool HILO> WQ_DEVICE void store_row_codes(const float* v, float inv, i
 
 template <class T, int GROUP, bool HILO, int ACT, int CPW>
 __global__ void __launch_bounds__(kRowThreads) quantize_rows(const T* __restrict__ x, int8_t* __restrict__ hi, int8_t* __restrict__ lo,
-                                                             float* __restrict__ scale, int k, int64_t ldx, const T* __restrict__ act_weight, float eps) {
+                                                             float* __restrict__ scale, int k, int64_t ldx, const T* __restrict__ act_weight, float eps,
+                                                             RowShift shift) {
     __shared__ float sum_slots[8], max_slots[8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t row = blockIdx.x;
-    const T* src = x + row * ldx;
+    const T* src = first_row(x, ldx, shift) + row * ldx;
     float amax = 0.f;
     if constexpr (CPW > 0) {
         float v[CPW][8];
@@ -291,78 +300,80 @@ static int persistent_ctas(int64_t warps_of_work) {
 }
 
 template <class T, int GROUP, int ACT>
-static int launch_blocks(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, const void* act_weight, float eps, cudaStream_t stream) {
+static int launch_blocks(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, const void* act_weight, float eps, const RowShift& shift,
+                         cudaStream_t stream) {
     auto src = static_cast<const T*>(x);
     auto aw = static_cast<const T*>(act_weight);
     if constexpr (ACT == kActRms) {
-        if (k <= 2048) quantize_blocks_rms<T, GROUP, 1><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps);
-        else if (k <= 4096) quantize_blocks_rms<T, GROUP, 2><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps);
-        else if (k <= 8192) quantize_blocks_rms<T, GROUP, 4><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps);
-        else if (k <= 16384) quantize_blocks_rms<T, GROUP, 8><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps);
-        else quantize_blocks_rms<T, GROUP, 0><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps);
+        if (k <= 2048) quantize_blocks_rms<T, GROUP, 1><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
+        else if (k <= 4096) quantize_blocks_rms<T, GROUP, 2><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
+        else if (k <= 8192) quantize_blocks_rms<T, GROUP, 4><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
+        else if (k <= 16384) quantize_blocks_rms<T, GROUP, 8><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
+        else quantize_blocks_rms<T, GROUP, 0><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
     } else {
         const int64_t items = int64_t(m) * ((k + kChunk - 1) / kChunk);
-        quantize_blocks_stream<T, GROUP, ACT><<<persistent_ctas((items + 1) / 2), 256, 0, stream>>>(src, q, scale, m, k, ldx);
+        quantize_blocks_stream<T, GROUP, ACT><<<persistent_ctas((items + 1) / 2), 256, 0, stream>>>(src, q, scale, m, k, ldx, shift);
     }
     return int(cudaGetLastError());
 }
 
 template <class T, int ACT>
-static int blocks_by_group(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, int group, const void* aw, float eps, cudaStream_t stream) {
+static int blocks_by_group(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, int group, const void* aw, float eps, const RowShift& shift,
+                           cudaStream_t stream) {
     switch (group) {
-        case 0: return launch_blocks<T, 0, ACT>(x, q, scale, m, k, ldx, aw, eps, stream);
-        case 16: return launch_blocks<T, 16, ACT>(x, q, scale, m, k, ldx, aw, eps, stream);
-        case 64: return launch_blocks<T, 64, ACT>(x, q, scale, m, k, ldx, aw, eps, stream);
-        case 256: return launch_blocks<T, 256, ACT>(x, q, scale, m, k, ldx, aw, eps, stream);
+        case 0: return launch_blocks<T, 0, ACT>(x, q, scale, m, k, ldx, aw, eps, shift, stream);
+        case 16: return launch_blocks<T, 16, ACT>(x, q, scale, m, k, ldx, aw, eps, shift, stream);
+        case 64: return launch_blocks<T, 64, ACT>(x, q, scale, m, k, ldx, aw, eps, shift, stream);
+        case 256: return launch_blocks<T, 256, ACT>(x, q, scale, m, k, ldx, aw, eps, shift, stream);
     }
     return -1;
 }
 
 template <class T>
 static int blocks_by_act(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, int group, int act, const void* aw, float eps,
-                         cudaStream_t stream) {
+                         const RowShift& shift, cudaStream_t stream) {
     switch (act) {
-        case kActNone: return blocks_by_group<T, kActNone>(x, q, scale, m, k, ldx, group, aw, eps, stream);
-        case kActRms: return blocks_by_group<T, kActRms>(x, q, scale, m, k, ldx, group, aw, eps, stream);
-        case kActSwiglu: return blocks_by_group<T, kActSwiglu>(x, q, scale, m, k, ldx, group, aw, eps, stream);
-        case kActGelu: return blocks_by_group<T, kActGelu>(x, q, scale, m, k, ldx, group, aw, eps, stream);
+        case kActNone: return blocks_by_group<T, kActNone>(x, q, scale, m, k, ldx, group, aw, eps, shift, stream);
+        case kActRms: return blocks_by_group<T, kActRms>(x, q, scale, m, k, ldx, group, aw, eps, shift, stream);
+        case kActSwiglu: return blocks_by_group<T, kActSwiglu>(x, q, scale, m, k, ldx, group, aw, eps, shift, stream);
+        case kActGelu: return blocks_by_group<T, kActGelu>(x, q, scale, m, k, ldx, group, aw, eps, shift, stream);
     }
     return -1;
 }
 
 template <class T, int GROUP, bool HILO, int ACT>
 static int launch_rows(const void* x, int8_t* hi, int8_t* lo, float* scale, int m, int k, int64_t ldx, const void* act_weight, float eps,
-                       cudaStream_t stream) {
+                       const RowShift& shift, cudaStream_t stream) {
     auto src = static_cast<const T*>(x);
     auto aw = static_cast<const T*>(act_weight);
-    if (k <= 2048) quantize_rows<T, GROUP, HILO, ACT, 1><<<m, kRowThreads, 0, stream>>>(src, hi, lo, scale, k, ldx, aw, eps);
-    else if (k <= 4096) quantize_rows<T, GROUP, HILO, ACT, 2><<<m, kRowThreads, 0, stream>>>(src, hi, lo, scale, k, ldx, aw, eps);
-    else if (k <= 8192) quantize_rows<T, GROUP, HILO, ACT, 4><<<m, kRowThreads, 0, stream>>>(src, hi, lo, scale, k, ldx, aw, eps);
-    else if (k <= 16384) quantize_rows<T, GROUP, HILO, ACT, 8><<<m, kRowThreads, 0, stream>>>(src, hi, lo, scale, k, ldx, aw, eps);
-    else quantize_rows<T, GROUP, HILO, ACT, 0><<<m, kRowThreads, 0, stream>>>(src, hi, lo, scale, k, ldx, aw, eps);
+    if (k <= 2048) quantize_rows<T, GROUP, HILO, ACT, 1><<<m, kRowThreads, 0, stream>>>(src, hi, lo, scale, k, ldx, aw, eps, shift);
+    else if (k <= 4096) quantize_rows<T, GROUP, HILO, ACT, 2><<<m, kRowThreads, 0, stream>>>(src, hi, lo, scale, k, ldx, aw, eps, shift);
+    else if (k <= 8192) quantize_rows<T, GROUP, HILO, ACT, 4><<<m, kRowThreads, 0, stream>>>(src, hi, lo, scale, k, ldx, aw, eps, shift);
+    else if (k <= 16384) quantize_rows<T, GROUP, HILO, ACT, 8><<<m, kRowThreads, 0, stream>>>(src, hi, lo, scale, k, ldx, aw, eps, shift);
+    else quantize_rows<T, GROUP, HILO, ACT, 0><<<m, kRowThreads, 0, stream>>>(src, hi, lo, scale, k, ldx, aw, eps, shift);
     return int(cudaGetLastError());
 }
 
 template <class T, bool HILO, int ACT>
 static int rows_by_group(const void* x, int8_t* hi, int8_t* lo, float* scale, int m, int k, int64_t ldx, int group, const void* aw, float eps,
-                         cudaStream_t stream) {
+                         const RowShift& shift, cudaStream_t stream) {
     switch (group) {
-        case 0: return launch_rows<T, 0, HILO, ACT>(x, hi, lo, scale, m, k, ldx, aw, eps, stream);
-        case 16: return launch_rows<T, 16, HILO, ACT>(x, hi, lo, scale, m, k, ldx, aw, eps, stream);
-        case 64: return launch_rows<T, 64, HILO, ACT>(x, hi, lo, scale, m, k, ldx, aw, eps, stream);
-        case 256: return launch_rows<T, 256, HILO, ACT>(x, hi, lo, scale, m, k, ldx, aw, eps, stream);
+        case 0: return launch_rows<T, 0, HILO, ACT>(x, hi, lo, scale, m, k, ldx, aw, eps, shift, stream);
+        case 16: return launch_rows<T, 16, HILO, ACT>(x, hi, lo, scale, m, k, ldx, aw, eps, shift, stream);
+        case 64: return launch_rows<T, 64, HILO, ACT>(x, hi, lo, scale, m, k, ldx, aw, eps, shift, stream);
+        case 256: return launch_rows<T, 256, HILO, ACT>(x, hi, lo, scale, m, k, ldx, aw, eps, shift, stream);
     }
     return -1;
 }
 
 template <class T, bool HILO>
 static int rows_by_act(const void* x, int8_t* hi, int8_t* lo, float* scale, int m, int k, int64_t ldx, int group, int act, const void* aw, float eps,
-                       cudaStream_t stream) {
+                       const RowShift& shift, cudaStream_t stream) {
     switch (act) {
-        case kActNone: return rows_by_group<T, HILO, kActNone>(x, hi, lo, scale, m, k, ldx, group, aw, eps, stream);
-        case kActRms: return rows_by_group<T, HILO, kActRms>(x, hi, lo, scale, m, k, ldx, group, aw, eps, stream);
-        case kActSwiglu: return rows_by_group<T, HILO, kActSwiglu>(x, hi, lo, scale, m, k, ldx, group, aw, eps, stream);
-        case kActGelu: return rows_by_group<T, HILO, kActGelu>(x, hi, lo, scale, m, k, ldx, group, aw, eps, stream);
+        case kActNone: return rows_by_group<T, HILO, kActNone>(x, hi, lo, scale, m, k, ldx, group, aw, eps, shift, stream);
+        case kActRms: return rows_by_group<T, HILO, kActRms>(x, hi, lo, scale, m, k, ldx, group, aw, eps, shift, stream);
+        case kActSwiglu: return rows_by_group<T, HILO, kActSwiglu>(x, hi, lo, scale, m, k, ldx, group, aw, eps, shift, stream);
+        case kActGelu: return rows_by_group<T, HILO, kActGelu>(x, hi, lo, scale, m, k, ldx, group, aw, eps, shift, stream);
     }
     return -1;
 }
@@ -412,29 +423,52 @@ static int rotate_by_group(const void* x, void* out, int m, int k, int64_t ldx, 
 
 using namespace wq;
 
-WQ_API int wq8_quantize_blocks(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, int dtype, int group, int act,
-                               const void* act_weight, float eps, float* /*inv_rms: rows of any K are handled inside one kernel*/, cudaStream_t stream) {
+static int quantize_blocks_entry(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, int dtype, int group, int act,
+                                 const void* act_weight, float eps, const RowShift& shift, cudaStream_t stream) {
     if (m <= 0) return 0;
     if (k <= 0 || k % 8 || (group && k % group)) return -2;
-    if (dtype == 0) return blocks_by_act<__half>(x, q, scale, m, k, ldx, group, act, act_weight, eps, stream);
-    if (dtype == 1) return blocks_by_act<bf16>(x, q, scale, m, k, ldx, group, act, act_weight, eps, stream);
+    if (dtype == 0) return blocks_by_act<__half>(x, q, scale, m, k, ldx, group, act, act_weight, eps, shift, stream);
+    if (dtype == 1) return blocks_by_act<bf16>(x, q, scale, m, k, ldx, group, act, act_weight, eps, shift, stream);
     if (dtype != 2 || act) return -1;
-    return blocks_by_group<float, kActNone>(x, q, scale, m, k, ldx, group, nullptr, 0.f, stream);
+    return blocks_by_group<float, kActNone>(x, q, scale, m, k, ldx, group, nullptr, 0.f, shift, stream);
+}
+
+static int quantize_entry(const void* x, int8_t* hi, int8_t* lo, float* scale, int m, int k, int64_t ldx, int dtype, int group, int act,
+                          const void* act_weight, float eps, const RowShift& shift, cudaStream_t stream) {
+    if (m <= 0) return 0;
+    if (k <= 0 || k % 8 || (group && k % group)) return -2;
+    if (dtype == 0)
+        return lo ? rows_by_act<__half, true>(x, hi, lo, scale, m, k, ldx, group, act, act_weight, eps, shift, stream)
+                  : rows_by_act<__half, false>(x, hi, lo, scale, m, k, ldx, group, act, act_weight, eps, shift, stream);
+    if (dtype == 1)
+        return lo ? rows_by_act<bf16, true>(x, hi, lo, scale, m, k, ldx, group, act, act_weight, eps, shift, stream)
+                  : rows_by_act<bf16, false>(x, hi, lo, scale, m, k, ldx, group, act, act_weight, eps, shift, stream);
+    if (dtype != 2 || act) return -1;
+    return lo ? rows_by_group<float, true, kActNone>(x, hi, lo, scale, m, k, ldx, group, nullptr, 0.f, shift, stream)
+              : rows_by_group<float, false, kActNone>(x, hi, lo, scale, m, k, ldx, group, nullptr, 0.f, shift, stream);
+}
+
+WQ_API int wq8_quantize_blocks(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, int dtype, int group, int act,
+                               const void* act_weight, float eps, float* /*inv_rms: rows of any K are handled inside one kernel*/, cudaStream_t stream) {
+    return quantize_blocks_entry(x, q, scale, m, k, ldx, dtype, group, act, act_weight, eps, RowShift{nullptr, 0, 0}, stream);
+}
+
+// wq8_quantize_blocks reading rows first + counter[0] * step ... of x (the outputs start at row 0): counter on the GPU, read at run time.
+WQ_API int wq8_quantize_blocks_at(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, int dtype, int group, int act,
+                                  const void* act_weight, float eps, float* /*inv_rms*/, const long long* counter, long long first, long long step,
+                                  cudaStream_t stream) {
+    return quantize_blocks_entry(x, q, scale, m, k, ldx, dtype, group, act, act_weight, eps, RowShift{counter, first, step}, stream);
 }
 
 WQ_API int wq8_quantize(const void* x, int8_t* hi, int8_t* lo, float* scale, int m, int k, int64_t ldx, int dtype, int group, int act,
                         const void* act_weight, float eps, cudaStream_t stream) {
-    if (m <= 0) return 0;
-    if (k <= 0 || k % 8 || (group && k % group)) return -2;
-    if (dtype == 0)
-        return lo ? rows_by_act<__half, true>(x, hi, lo, scale, m, k, ldx, group, act, act_weight, eps, stream)
-                  : rows_by_act<__half, false>(x, hi, lo, scale, m, k, ldx, group, act, act_weight, eps, stream);
-    if (dtype == 1)
-        return lo ? rows_by_act<bf16, true>(x, hi, lo, scale, m, k, ldx, group, act, act_weight, eps, stream)
-                  : rows_by_act<bf16, false>(x, hi, lo, scale, m, k, ldx, group, act, act_weight, eps, stream);
-    if (dtype != 2 || act) return -1;
-    return lo ? rows_by_group<float, true, kActNone>(x, hi, lo, scale, m, k, ldx, group, nullptr, 0.f, stream)
-              : rows_by_group<float, false, kActNone>(x, hi, lo, scale, m, k, ldx, group, nullptr, 0.f, stream);
+    return quantize_entry(x, hi, lo, scale, m, k, ldx, dtype, group, act, act_weight, eps, RowShift{nullptr, 0, 0}, stream);
+}
+
+// wq8_quantize reading rows first + counter[0] * step ... of x: counter on the GPU, read at run time.
+WQ_API int wq8_quantize_at(const void* x, int8_t* hi, int8_t* lo, float* scale, int m, int k, int64_t ldx, int dtype, int group, int act,
+                           const void* act_weight, float eps, const long long* counter, long long first, long long step, cudaStream_t stream) {
+    return quantize_entry(x, hi, lo, scale, m, k, ldx, dtype, group, act, act_weight, eps, RowShift{counter, first, step}, stream);
 }
 
 WQ_API int wq8_transform_rows(const void* x, void* out, int m, int k, int64_t ldx, int dtype, int group, int act, const void* act_weight, float eps,

@@ -907,13 +907,12 @@ WQ_API void wq8_small_workspace(int m, int n, int k, int sms, int64_t* sizes) {
 WQ_API int wq8_small(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale, void* y,
                      int m, int n, int k, int dtype, int sms, float* slots, int* counters, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
-    if (k <= 0 || k % 64 || m > 32 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return -2;
+    // every kernel below reads x and w with 16-byte loads (or TMA boxes): unaligned operands are refused, never launched
+    if (k <= 0 || k % 64 || m > 32 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -2;
     if (dtype != 0 && dtype != 1) return -1;
-    if ((reinterpret_cast<uintptr_t>(w) & 15) == 0) {
-        const int rows = plan_bulk(m, n, k, sms);
-        if (rows && dtype == 0) return launch_bulk<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
-        if (rows) return launch_bulk<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
-    }
+    const int rows = plan_bulk(m, n, k, sms);
+    if (rows && dtype == 0) return launch_bulk<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
+    if (rows) return launch_bulk<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
     StreamPlan p = plan_stream(n, k, sms, true);
     if (p.splits > 1 && (!slots || !counters)) p.splits = 1;
     if (dtype == 0) return launch_stream<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, slots, counters, stream);
@@ -934,6 +933,8 @@ WQ_API int wq8_gemv_lines(const void* x, int64_t ldx, const int8_t* w, const flo
         if (dtype == 0) return launch_stream<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, nullptr, nullptr, stream);
         return launch_stream<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, nullptr, nullptr, stream);
     }
+    // the general kernel reads four weight bytes and four activations (8 bytes) per lane and step
+    if (ldx % 4 || (reinterpret_cast<uintptr_t>(x) & 7) || (reinterpret_cast<uintptr_t>(w) & 3)) return -2;
     if (dtype == 0) return launch_cores<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, stream);
     return launch_cores<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, stream);
 }
@@ -982,8 +983,9 @@ static unsigned char* static_scratch_address(int* error) {
 
 }  // namespace wq
 
-// Same linear as wq8_small (at most 32 tokens, K multiple of 64, x rows 16-byte aligned), same values, no scratch arguments and no
-// allocation of any kind: the K-split partial sums and tile counters use the library's own static device buffer.
+// Same linear as wq8_small (at most 32 tokens, K multiple of 64, x rows and w 16-byte aligned) with the same kernel choice, hence the
+// same values bit for bit; no scratch arguments and no allocation of any kind: shapes that run the ring kernel need no scratch at all,
+// the others keep their K-split partial sums and tile counters in the library's own static device buffer.
 // Returns -5 when the shape's scratch would not fit that buffer (use wq8_small with caller scratch then); other codes as wq8_small.
 // Calls share the one buffer per device: two calls whose kernels may overlap on the GPU (different streams, or one stream of a graph with
 // parallel branches) race on it -- keep them on one stream, or give the others caller scratch through wq8_small.  The buffer keeps what
@@ -991,8 +993,11 @@ static unsigned char* static_scratch_address(int* error) {
 WQ_API int wq8_small_static(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
                             void* y, int m, int n, int k, int dtype, int sms, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
-    if (k <= 0 || k % 64 || m > 32 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return -2;
+    if (k <= 0 || k % 64 || m > 32 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -2;
     if (dtype != 0 && dtype != 1) return -1;
+    const int rows = plan_bulk(m, n, k, sms);  // the ring kernel: no scratch at all
+    if (rows && dtype == 0) return launch_bulk<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
+    if (rows) return launch_bulk<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
     const StreamPlan p = plan_stream(n, k, sms, true);
     float* slots = nullptr;
     int* counters = nullptr;

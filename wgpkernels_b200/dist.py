@@ -33,13 +33,30 @@ def shard_bounds(n, world_size, rank, multiple=8):
     return start, stop
 
 
-def worth_sharding(m, n, k, world_size, tops=2500.0, link_gbs=770.0, output_bytes=2):
-    """Estimated times in ms of the unsharded linear and of the sharded one with its all-gather, and whether sharding wins.
-    tops: sustained INT8 throughput of one GPU; link_gbs: per-direction NVLink bandwidth of one GPU."""
+# Measured on B200 (one node, NVSwitch): effective INT8 throughput of the block path's GEMM on one GPU, the replicated activation
+# quantizer's HBM rate, and the bytes per second one GPU receives from its peers' TMA stores.
+MEASURED_TOPS, MEASURED_QUANTIZER_GBS, MEASURED_LINK_GBS = 1800.0, 2800.0, 770.0
+
+
+def worth_sharding(m, n, k, world_size, tops=MEASURED_TOPS, link_gbs=MEASURED_LINK_GBS, output_bytes=2, quantizer_gbs=MEASURED_QUANTIZER_GBS):
+    """Estimated times in ms of the linear on one GPU and sharded over `world_size` GPUs with the full output replicated on every rank,
+    and which number of ranks (a power of two up to world_size) is the fastest.  Sharded: the GEMM shrinks by g, the activation
+    quantizer does not (every rank quantizes all of x), and every rank receives (g - 1) / g of the (M, N) output over NVLink, which
+    the fused gather overlaps with the GEMM: step = quantizer + max(GEMM / g, incoming bytes / link rate)."""
+    quantize_ms = 3.0 * m * k / (quantizer_gbs * 1e9) * 1e3
     gemm_ms = 2.0 * m * n * k / (tops * 1e12) * 1e3
+
+    def step_ms(g):
+        gather = (g - 1) / g * m * n * output_bytes / (link_gbs * 1e9) * 1e3
+        return quantize_ms + max(gemm_ms / g, gather)
+
+    candidates = [1]
+    while candidates[-1] * 2 <= world_size:
+        candidates.append(candidates[-1] * 2)
+    best = min(candidates, key=lambda g: (step_ms(g), g))
     gather_ms = (world_size - 1) / world_size * m * n * output_bytes / (link_gbs * 1e9) * 1e3
-    sharded_ms = max(gemm_ms / world_size, gather_ms)  # the gather of finished row bands overlaps the GEMM of the next ones
-    return {"single_ms": gemm_ms, "sharded_ms": sharded_ms, "gather_ms": gather_ms, "shard": sharded_ms < gemm_ms}
+    return {"single_ms": step_ms(1), "sharded_ms": step_ms(world_size), "gather_ms": gather_ms, "shard": step_ms(world_size) < step_ms(1),
+            "best_ranks": best, "best_ms": step_ms(best), "bound": "nvlink" if gather_ms > gemm_ms / world_size else "tensor"}
 
 
 @dataclass
@@ -98,6 +115,9 @@ class ShardedLinear:
         """(M, N) on every rank, each rank's GEMM writing its columns into all ranks' buffers.  The result is this layer's own buffer for
         (M, dtype): it is overwritten by the next call with the same M.  residual / residual_scale: the rank's own columns, (M, N / g)
         with any row stride and (N / g)."""
+        mode = kwargs.setdefault("mode", "block")
+        if mode not in ("block", "exact", "row"):
+            raise ValueError(f"the fused gather runs the 'block', 'exact' or 'row' path (every rank the same one), not {mode!r}")
         own, views, token = self.symmetric_output(x.shape[0], x.dtype, x.device)
         # every rank has finished reading the previous contents of the buffers (this rank's kernels that read them precede on its stream)
         dist.all_reduce(token, group=self.group)

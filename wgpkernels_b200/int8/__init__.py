@@ -57,8 +57,8 @@ def weight_groups_supported():
 
 
 def segments_supported():
-    """Whether the loaded library computes several linears of one input in one GEMM."""
-    return False
+    """Whether the loaded library computes several linears of one input in one GEMM launch (wq8_gemm_segments)."""
+    return _lib is not None and hasattr(_lib, "wq8_gemm_segments")
 
 
 def _require():
@@ -76,6 +76,10 @@ _SIGNATURES = {
     "wq8_rotate_groups": "vviiliiv",
     "wq8_gemm": "vvvvvvvvviiiiiiivvv",
     "wq8_gemm_multi": "vvvvvvvlvviliiiiiivv",
+    "wq8_gemm_segments": "vvvvvvviiiiiiiivvv",
+    "wq8_gemm_at": "vvvvvvvvviiiiiiivvvllllllv",
+    "wq8_quantize_at": "vvvviiliiivfvllv",
+    "wq8_quantize_blocks_at": "vvviiliiivfvvllv",
     "wq8_gemm_workspace": "iiiiiiv->",
     "wq8_gemm_select": "iiiii",
     "wq8_small": "vlvvvvvviiiiivvv",
@@ -86,9 +90,10 @@ _SIGNATURES = {
     "wq8_l2_flush": "ilv",
     "wq8_l2_flush_release": "->",
     "wq8_debug_block_sums": "vvviiiiv",
+    "wq8_debug_wait_probe": "livv",
     "wq8_debug_status": "",
 }
-_CTYPES = {"v": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_int64, "f": ctypes.c_float}
+_CTYPES = {"v": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_int64, "f": ctypes.c_float}  # "l" also carries long long
 
 
 def _bind(handle):
@@ -257,13 +262,14 @@ def prepare(x, group=0, path="block", act=None, act_weight=None, eps=0.0):
 # ---------------------------------------------------------------------------------------------------------------------
 # (variant, split) candidates per mode; the first is the untuned default.  The variant numbers keep the reference's MODE meaning
 # (row 0/2/6, exact 1/7, block 10/11, block+g 12/13, exact+g 14); what differs between the variants of a mode is this library's own:
-# 10 / 12 / 14 keep the accumulators in tensor memory biased for the INT32 -> FP32 conversion, 11 / 13 add the bias with an integer add;
-# 15 / 16 are 10 / 11 with tiles of 128 instead of 256 output channels (four accumulator buffers): the better choice for small products.
-_CANDIDATES = {"row": ((0, 0),), "exact": ((1, 0),), "block": ((10, 0), (11, 0), (15, 0), (16, 0)), "exact+g": ((14, 0),),
-               "block+g": ((12, 0), (13, 0))}
-_MODES = {0: "row", 2: "row", 6: "row", 1: "exact", 7: "exact", 10: "block", 11: "block", 15: "block", 16: "block", 12: "block+g", 13: "block+g",
-          14: "exact+g"}
-_TUNING_VERSION = 1
+# 10 and 12 work on tiles of 256 output channels (two accumulator buffers in tensor memory) with sixteen drain warps, 20 and 22 are the
+# same with eight drain warps (fewer instructions per output, fewer warps to hide latencies), 15 and 13 work on tiles of 128 channels
+# (four buffers, more tiles: the better choice for small products); 11 and 16 are accepted as other names of 10 and 15.
+_CANDIDATES = {"row": ((0, 0),), "exact": ((1, 0),), "block": ((10, 0), (20, 0), (15, 0)), "exact+g": ((14, 0),),
+               "block+g": ((12, 0), (22, 0), (13, 0))}
+_MODES = {0: "row", 2: "row", 6: "row", 1: "exact", 7: "exact", 10: "block", 11: "block", 15: "block", 16: "block", 20: "block", 12: "block+g",
+          13: "block+g", 22: "block+g", 14: "exact+g"}
+_TUNING_VERSION = 2
 _TUNING_PATH = Path(os.environ.get("WGPKERNELS_B200_CACHE") or Path.home() / ".cache" / "wgpkernels_b200" / "int8_tuning.json")
 _tuned = None
 _path_tuning = ContextVar("wgpkernels_b200_int8_path_tuning", default=False)
@@ -363,12 +369,11 @@ def _best_of(launches, device):
     return best
 
 
-def _tuned_config(a, a_lo, sa, b, sb, bias, y, mode):
+def _tuned_config(rows, n, k, device, mode, make_launch):
     """((variant, split), tuned?) for the bucket of this shape.  Known buckets come from the cache; a mode with one candidate needs no
-    timing; while a CUDA graph is captured or compiled the first candidate is used and nothing is recorded; otherwise the candidates are
-    timed on this call's operands (y is overwritten) and the winner is stored."""
-    rows, n, k = a.shape[0], b.shape[0], a.shape[1]
-    key = "|".join((mode, f"{_rows_bucket(rows)}x{n}x{k}", _device_name(b.device.index)))
+    timing; while a CUDA graph is captured or compiled the first candidate is used and nothing is recorded; otherwise every candidate is
+    timed through make_launch((variant, split)) -> callable (which may overwrite the output it was given) and the winner is stored."""
+    key = "|".join((mode, f"{_rows_bucket(rows)}x{n}x{k}", _device_name(device.index)))
     known = _cache().get(key)
     if known is not None:
         return tuple(known), True
@@ -383,12 +388,7 @@ def _tuned_config(a, a_lo, sa, b, sb, bias, y, mode):
     began = time.time()
     if verbose:
         print(f"[WGPKernels-B200] Autotuning {what}...", flush=True)
-
-    def launcher(option):
-        variant, split = option
-        return lambda: gemm(a, a_lo, sa, b, sb, bias, y.dtype, split, variant, y)
-
-    times = _best_of({option: launcher(option) for option in options}, b.device)
+    times = _best_of({option: make_launch(option) for option in options}, device)
     winner = min(options, key=lambda option: (times[option], option))
     _tuned[key] = list(winner)
     _save_cache()
@@ -401,15 +401,14 @@ def _tuned_config(a, a_lo, sa, b, sb, bias, y, mode):
 _plans = {}  # (mode, M, N, K, device) -> (variant, split, workspace bytes, counter bytes)
 
 
-def _plan(a, a_lo, sa, b, sb, bias, y, mode, scratch_output):
+def _plan(m, n, k, device, mode, make_launch):
     """(variant, split, workspace bytes, counter bytes) of a GEMM of this exact shape; remembered once it comes from a tuned choice.
-    scratch_output: y holds data the caller still needs (a residual), so the tuner gets an output of its own."""
-    signature = (mode, a.shape[0], b.shape[0], a.shape[1], b.device.index)
+    make_launch is only called when candidates have to be timed (it is where a scratch output gets allocated, if one is needed)."""
+    signature = (mode, m, n, k, device.index)
     if signature in _plans:
         return _plans[signature]
-    target = torch.empty_like(y) if scratch_output else y
-    (variant, split), final = _tuned_config(a, a_lo, sa, b, sb, bias, target, mode)
-    _require().wq8_gemm_workspace(a.shape[0], b.shape[0], a.shape[1], variant, _sm_count(b.device), split, _sizes)
+    (variant, split), final = _tuned_config(m, n, k, device, mode, make_launch)
+    _require().wq8_gemm_workspace(m, n, k, variant, _sm_count(device), split, _sizes)
     result = (variant, split, _sizes[0], _sizes[1])
     if final:
         _plans[signature] = result
@@ -456,9 +455,19 @@ def gemm(a, a_lo, sa, b, sb, bias, out_dtype, split=None, variant=None, out=None
             if mode == "row":
                 raise ValueError("Weights with per-(n, k-block) scales run the 'block' or 'exact' path")
             mode += "+g"
-        tuning_y = torch.empty((m, n), dtype=out_dtype, device=a.device) if strided else y  # the tuner may overwrite its output
-        variant, split, workspace_bytes, counter_bytes = _plan(a, a_lo, sa, b, sb, bias, tuning_y, mode, residual is not None and not strided)
-        del tuning_y
+
+        scratch = []  # the tuner overwrites its output: it gets one of its own when y is a view, several views or holds the residual
+
+        def make_launch(option):
+            if strided or residual is not None:
+                if not scratch:
+                    scratch.append(torch.empty((m, n), dtype=out_dtype, device=a.device))
+                target = scratch[0]
+            else:
+                target = y
+            return lambda: gemm(a, a_lo, sa, b, sb, bias, out_dtype, option[1], option[0], target)
+
+        variant, split, workspace_bytes, counter_bytes = _plan(m, n, k, a.device, mode, make_launch)
     else:
         split = 1 if split is None else split
         lib.wq8_gemm_workspace(m, n, k, variant, sms, split, _sizes)
@@ -539,10 +548,38 @@ def linear_prepared(prepared, weight, scale, bias=None, residual=None, residual_
     return few_tokens(prepared.x, weight, scale, bias, residual, residual_scale, out)
 
 
+def _pointer_table(tensors):
+    return (ctypes.c_void_p * 4)(*[None if t is None else t.data_ptr() for t in tensors])
+
+
 def linear_prepared_segments(prepared, weights, scales, biases, outputs):
-    """outputs[s] = prepared @ (weights[s] * scales[s]).T + biases[s] for several weights of one prepared input."""
-    for weight, scale, bias, out in zip(weights, scales, biases, outputs):
-        linear_prepared(prepared, weight, scale, bias, out=out)
+    """outputs[s] = prepared @ (weights[s] * scales[s]).T + biases[s] for 1 to 4 linears of one 'exact', 'block' or 'row' preparation in
+    ONE GEMM launch that reads the prepared input once: weights INT8 (rows, K), each contiguous, all of the same shape; scales FP32
+    (rows,); biases in the output dtype or None; outputs (M, rows) contiguous in the prepared dtype, rows a multiple of 8.  Each output
+    is bit for bit what linear_prepared gives on that weight with the same tile variant (a column tile never straddles two weights).
+    The tile variant is chosen once for N = count * rows, timed on the launch itself."""
+    lib = _require()
+    a, count, rows = prepared.x, len(weights), weights[0].shape[0]
+    if not 1 <= count <= 4 or rows % 8 or not (len(scales) == len(biases) == len(outputs) == count):
+        raise ValueError("1 to 4 weights of the same shape, rows a multiple of 8, one scale, bias (or None) and output for each")
+    if prepared.path not in ("exact", "block", "row"):
+        raise ValueError("segments run the 'exact', 'block' or 'row' path")
+    for weight, scale, out in zip(weights, scales, outputs):
+        if scale.dim() != 1:
+            raise ValueError("Weights with per-(n, k-block) scales cannot share a launch")
+        if tuple(weight.shape) != tuple(weights[0].shape) or not weight.is_contiguous() or not out.is_contiguous() or tuple(out.shape) != (a.shape[0], rows):
+            raise ValueError("every weight (rows, K) and output (M, rows) must be contiguous and of the same shape")
+    m, k = a.shape
+    stream = _stream(a.device)
+    tables = [_pointer_table(t) for t in (weights, scales, biases, outputs)]
+
+    def launch(variant, split, workspace):
+        _check(lib.wq8_gemm_segments(a.data_ptr(), _ptr(prepared.lo), prepared.scale.data_ptr(), *tables, count, rows, m, k, _DTYPES[prepared.dtype],
+                                     variant, _sm_count(a.device), split, _ptr(workspace), None, stream))
+
+    variant, split, workspace_bytes, _ = _plan(m, count * rows, k, a.device, prepared.path, lambda option: lambda: launch(option[0], option[1], None))
+    workspace = torch.empty(workspace_bytes, dtype=torch.uint8, device=a.device) if workspace_bytes else None
+    launch(variant, split, workspace)
     return outputs
 
 
@@ -780,13 +817,12 @@ def debug_status():
     return _require().wq8_debug_status()
 
 
-def debug_mma_peak(kind="i8", groups=4000, random_operands=True, device=None):
-    """Issue-rate probe of the tensor pipe on the current device: (TOPS of the whole GPU, SM MHz during the probe, clocks per group of
-    four M128 N256 MMAs).  kind "i8" (tcgen05 kind::i8) or "bf16" (kind::f16).  A measurement tool: allocates and synchronizes."""
+def debug_wait_probe(clocks=2_000_000, code=9, device=None):
+    """Runs one bounded wait on a barrier that nothing completes, with a limit of `clocks` SM clocks: (what the kernel reported --
+    1 completed, 2 gave up --, the status word afterwards).  The give-up path of the library's waits, exercised without a fault."""
     lib = _require()
-    lib.wq8_debug_mma_peak.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
-    lib.wq8_debug_mma_peak.restype = ctypes.c_int
-    results = (ctypes.c_double * 3)()
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
-    _check(lib.wq8_debug_mma_peak(0 if kind == "i8" else 1, -groups if random_operands else groups, _sm_count(device), results))
-    return results[0], results[1], results[2]
+    returned = torch.zeros(1, dtype=torch.int32, device=device)
+    _check(lib.wq8_debug_wait_probe(clocks, code, returned.data_ptr(), _stream(device)))
+    status = lib.wq8_debug_status()
+    return int(returned.item()), status
