@@ -140,7 +140,8 @@ int wq8_gemm_multi(const int8_t* a, const int8_t* a_lo, const float* sa, const i
 
 /* The few-token linear (at most 8 tokens, K multiple of 128) on INT8 tensor cores with the weights as they are: the activations are
  * first split into three planes of signed 7-bit digits per 128 values with one power of two (exact for every value within 2^14 of the
- * largest of its 128), into `workspace` (wq8_stream_planes_workspace() bytes, 16-byte aligned; 0 = the shape is not supported, use
+ * largest of its 128; smaller ones are rounded to nearest with an absolute error of at most 2^-21 of that largest value, unbiased),
+ * into `workspace` (wq8_stream_planes_workspace() bytes, 16-byte aligned; 0 = the shape is not supported, use
  * wq8_gemv_lines / wq8_small).  Same arguments and error codes as wq8_small otherwise.  The reference has no counterpart: its few-token
  * kernels (and wq8_gemv_lines / wq8_small here) convert every weight byte to BF16 / FP16 instead, which bounds them below the HBM rate. */
 int64_t wq8_stream_planes_workspace(int m, int n, int k, int sms);

@@ -27,7 +27,10 @@ def test_sharding_policy():
     assert wide["gather_ms"] > wide["single_ms"] / 8  # config 1: the gather, not the GEMM, is what is left
     deep = wdist.worth_sharding(32760, 5120, 13824, 2)
     assert deep["shard"]
-    assert not wdist.worth_sharding(64, 5120, 512, 8)["shard"]
+    assert wide["bound"] == "nvlink" and wide["best_ranks"] < 8  # replicating a 1 GB output to 8 GPUs loses to fewer ranks
+    assert deep["best_ranks"] == 2
+    small = wdist.worth_sharding(64, 5120, 512, 8)
+    assert small["best_ms"] <= small["single_ms"]
 
 
 def test_unshard():
@@ -52,8 +55,8 @@ def _rank_main(rank, world_size, port, failures):
         c = workloads.make("c0", rows=24)
         c.weight, c.scale, c.bias = c.weight[:256].contiguous(), c.scale[:256].contiguous(), c.bias[:256].contiguous()
 
-        def cpu_linear(x, weight, scale, bias, residual=None, residual_scale=None, **kwargs):
-            return oracle.linear("block", x, weight.numpy(), scale.numpy(), bias, residual=residual, rscale=residual_scale, **kwargs)
+        def cpu_linear(x, weight, scale, bias, residual=None, residual_scale=None, mode="block", **kwargs):
+            return oracle.linear(mode, x, weight.numpy(), scale.numpy(), bias, residual=residual, rscale=residual_scale, **kwargs)
 
         full = cpu_linear(c.x, c.weight, c.scale, c.bias)
         layer = wdist.ShardedLinear.from_full(c.weight, c.scale, c.bias, linear=cpu_linear)
@@ -83,6 +86,11 @@ def _rank_main(rank, world_size, port, failures):
         fused_layer.symmetric_output = lambda m, dtype, device: (views[rank], views, torch.zeros(1))
         returned = fused_layer(c.x, gather="fused", out=torch.empty(1))  # a caller's `out` is ignored: the result is the layer's buffer
         assert returned is views[rank]
+        try:  # the fused gather never times paths: a few-token path (or none given and a tuner picking one) is refused
+            fused_layer(c.x, gather="fused", mode="lines")
+            raise AssertionError("mode='lines' must be refused by the fused gather")
+        except ValueError:
+            pass
         assert order == [(rank + d) % world_size for d in range(world_size)]
         for view in views:
             assert torch.equal(view[:, fused_layer.start:fused_layer.stop], full[:, fused_layer.start:fused_layer.stop])

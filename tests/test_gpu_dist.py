@@ -1,5 +1,6 @@
-"""N-sharded linear on two GPUs of one box (skipped with fewer): the fused gather, in which every rank's GEMM writes its output
-columns into all ranks' symmetric-memory buffers, and the NCCL all-gather, both against the unsharded linear on the same operands."""
+"""N-sharded linear on 2, 4 and 8 GPUs of one box (as many as the box has; skipped with one): the fused gather, in which every rank's
+GEMM writes its output columns into all ranks' symmetric-memory buffers, and the NCCL all-gather, both bit for bit against the unsharded
+linear on the same operands; the row-sharded host pipeline against the same."""
 import os
 import socket
 import subprocess
@@ -13,6 +14,7 @@ pytestmark = pytest.mark.gpu
 WORKER = r'''
 import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["WQ_REPO"])
+os.environ["WGPKERNELS_B200_CACHE"] = os.path.join(os.environ["WQ_TMP"], "tuning_" + os.environ["RANK"] + ".json")  # read at import
 from wgpkernels_b200 import int8 as wq, dist as wdist, workloads
 rank = int(os.environ["RANK"]); torch.cuda.set_device(rank); device = torch.device("cuda", rank)
 dist.init_process_group("nccl", device_id=device)
@@ -30,15 +32,48 @@ for name, rows in (("c1", 1000), ("c2", 700), ("c4", 520)):
                     residual_scale=rscale)
         torch.cuda.synchronize()
         assert got.shape == expected.shape and torch.equal(got, expected), (name, gather, rank, float((got.float() - expected.float()).abs().max()))
+    for mode in ("exact", "row"):
+        if full.scale.dim() == 2 and mode == "row":
+            continue
+        expected = wq.linear(full.x, full.weight, full.scale, full.bias, mode=mode, act=full.act, act_weight=full.act_weight, eps=full.eps,
+                             residual=full.residual, residual_scale=full.residual_scale)
+        got = layer(full.x, gather="fused", mode=mode, act=full.act, act_weight=full.act_weight, eps=full.eps, residual=residual, residual_scale=rscale)
+        torch.cuda.synchronize()
+        assert torch.equal(got, expected), (name, mode, rank)
+    try:
+        layer(full.x[:4], gather="fused", mode="lines")
+        raise AssertionError("few-token paths must be refused by the fused gather")
+    except ValueError:
+        pass
     assert wq.debug_status() == 0
+# host pipeline, rows sharded over the ranks: every rank's band of the output equals the unsharded linear's
+from wgpkernels_b200.host import ShardedHostLinear
+full = workloads.make("c1", rows=1000).to(device)
+expected = wq.linear(full.x, full.weight, full.scale, full.bias, mode="block", act=full.act, act_weight=full.act_weight, eps=full.eps)
+host = ShardedHostLinear(full.weight, full.scale, full.bias, rows=1000, k=full.k, dtype=full.x.dtype, chunk_rows=128, tag=os.environ["MASTER_PORT"])
+if rank == 0:
+    host.x.copy_(full.x.cpu())
+dist.barrier()
+host(mode="block", act=full.act, act_weight=full.act_weight, eps=full.eps)
+torch.cuda.synchronize()
+dist.barrier()
+assert torch.equal(host.y.to(device), expected), rank
+host.close()
 dist.barrier()
 dist.destroy_process_group()
 print(f"rank {rank} ok")
 '''
 
 
-@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_rank_fused_and_nccl_gather(tmp_path):
+def _world_sizes():
+    count = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    return [size for size in (2, 4, 8) if size <= count] or [2]
+
+
+@pytest.mark.parametrize("world", _world_sizes())
+def test_sharded_linear_equals_unsharded(tmp_path, world):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
     with socket.socket() as s:
@@ -46,8 +81,9 @@ def test_two_rank_fused_and_nccl_gather(tmp_path):
         port = s.getsockname()[1]
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     workers = []
-    for rank in range(2):
-        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WQ_REPO=repo)
+    for rank in range(world):
+        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WQ_REPO=repo,
+                   WQ_TMP=str(tmp_path))
         workers.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     outputs = []
     for worker in workers:

@@ -120,3 +120,74 @@ def test_errors(wq):
         wq.gemm(hi, None, row_scale, c.weight, c.scale, None, torch.bfloat16, 0, 99)
     with pytest.raises(ValueError):
         wq.linear(c.x, c.weight, c.scale, act="relu")
+
+
+def test_graph_loop_over_row_windows(wq):
+    """The use the *_at entry points exist for: ONE captured quantize + GEMM body replayed while a device counter advances walks a long
+    input window by window; the result equals the eager linear on the whole input."""
+    import ctypes
+    c = workloads.make("c0", rows=640).to("cuda")
+    window, n, k = 160, c.n, c.k
+    lib = wq._require()
+    expected = wq.linear(c.x, c.weight, c.scale, c.bias, mode="block")
+    out = torch.zeros_like(expected)
+    codes = torch.empty((window, k), dtype=torch.int8, device="cuda")
+    scales = torch.empty((window, k // 128), dtype=torch.float32, device="cuda")
+    counter = torch.zeros(1, dtype=torch.int64, device="cuda")
+    one = torch.ones(1, dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        stream = wq._stream(c.x.device)
+        assert lib.wq8_quantize_blocks_at(c.x.data_ptr(), codes.data_ptr(), scales.data_ptr(), window, k, c.x.stride(0), 1, 0, 0, None, 0.0, None,
+                                          counter.data_ptr(), 0, window, stream) == 0
+        assert lib.wq8_gemm_at(codes.data_ptr(), None, scales.data_ptr(), c.weight.data_ptr(), c.scale.data_ptr(), c.bias.data_ptr(), None, None,
+                               out.data_ptr(), window, n, k, 1, 10, 148, 0, None, None, counter.data_ptr(), 0, window, 0, 0, 0, 0, stream) == 0
+        counter.add_(one)
+    for _ in range(640 // window):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, expected)
+    assert wq.debug_status() == 0
+
+
+def test_row_bands_through_small_scratch(wq, monkeypatch):
+    """_gemm_path with a scratch limit that forces several bands of rows (three or more, the last one ragged), with a residual written
+    in place and with a list of destinations: identical to the one-band result."""
+    c = workloads.make("c2", rows=700).to("cuda")
+    kwargs = dict(act=c.act, act_weight=c.act_weight, eps=c.eps, residual_scale=c.residual_scale)
+    for mode in ("block", "exact"):
+        whole = wq.linear(c.x, c.weight, c.scale, c.bias, mode=mode, residual=c.residual, **kwargs)
+        monkeypatch.setattr(wq, "SCRATCH_BYTES", 256 * (c.k * (2 if mode == "exact" else 1) + 4 * (c.k // 128)))  # bands of 256 rows
+        assert wq._chunk_rows(c.k, mode) == 256
+        in_place = c.residual.clone()
+        banded = wq.linear(c.x, c.weight, c.scale, c.bias, mode=mode, residual=in_place, out=in_place, **kwargs)
+        assert banded.data_ptr() == in_place.data_ptr() and torch.equal(banded, whole), mode
+        wide = [torch.zeros((700, c.n + 64), dtype=c.x.dtype, device="cuda") for _ in range(2)]
+        wq.linear(c.x, c.weight, c.scale, c.bias, mode=mode, residual=c.residual, out=[t[:, 32:32 + c.n] for t in wide], **kwargs)
+        for t in wide:
+            assert torch.equal(t[:, 32:32 + c.n], whole) and not t[:, :32].any() and not t[:, 32 + c.n:].any()
+        monkeypatch.undo()
+
+
+@pytest.mark.parametrize("name,rows", [("c1", 1500), ("c2", 900), ("c4", 1100)])
+def test_config_bands_match_reference_library(wq, name, rows):
+    """Bands of the benchmark configurations (their outlier channels, input operations, group scales) against the reference's own CUDA
+    library on the same tensors: codes and scales bit for bit, outputs within 1e-3 relative Frobenius."""
+    from tests import reflib
+    c = workloads.make(name, rows=rows).to("cuda")
+    q, s = wq.quantize_blocks(c.x, 0, c.act, c.act_weight, c.eps)
+    q_ref, s_ref = reflib.quantize_blocks(c.x, 0, c.act, c.act_weight, c.eps)
+    assert torch.equal(q, q_ref) and torch.equal(s, s_ref)
+    grouped = c.scale.dim() == 2
+    y = wq.gemm(q, None, s, c.weight, c.scale, c.bias, c.x.dtype, mode="block", residual=c.residual, residual_scale=c.residual_scale)
+    y_ref = reflib.gemm(q_ref, None, s_ref, c.weight, c.scale, c.bias, c.x.dtype, 12 if grouped else 10, residual=c.residual,
+                        residual_scale=c.residual_scale)
+    assert rel(y, y_ref) < 1e-3, name
+    hi, lo, rs = wq.quantize(c.x, 0, True, c.act, c.act_weight, c.eps)
+    hi_ref, lo_ref, rs_ref = reflib.quantize(c.x, 0, True, c.act, c.act_weight, c.eps)
+    assert torch.equal(hi, hi_ref) and torch.equal(lo, lo_ref) and torch.equal(rs, rs_ref)
+    y = wq.gemm(hi, lo, rs, c.weight, c.scale, c.bias, c.x.dtype, mode="exact", residual=c.residual, residual_scale=c.residual_scale)
+    y_ref = reflib.gemm(hi_ref, lo_ref, rs_ref, c.weight, c.scale, c.bias, c.x.dtype, 14 if grouped else 1, residual=c.residual,
+                        residual_scale=c.residual_scale)
+    assert rel(y, y_ref) < 1e-3, name

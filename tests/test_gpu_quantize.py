@@ -135,3 +135,35 @@ def test_large_row_count(wq):
     q, s = wq.quantize_blocks(x)
     q_ref, s_ref = reflib.quantize_blocks(x)
     assert torch.equal(q, q_ref) and torch.equal(s, s_ref)
+
+
+@pytest.mark.parametrize("act", [None, "rms_norm", "gelu"])
+def test_quantizers_at_row_windows(wq, act):
+    """wq8_quantize_at / wq8_quantize_blocks_at: for several values of the device counter the codes and scales equal the plain entry
+    points' on the matching slice of input rows (the outputs always start at row 0)."""
+    total, m, k, first, step = 120, 20, 1024 + 128, 3, 25
+    x = make_x(total, k, act, torch.bfloat16, 21).cuda()
+    w = weight_of(k, act, torch.bfloat16, 22)
+    w = None if w is None else w.cuda()
+    lib, stream = wq._require(), wq._stream(x.device)
+    acts = {None: 0, "rms_norm": 1, "gelu": 3}
+    for count in (0, 1, 3):
+        counter = torch.tensor([count], dtype=torch.int64, device="cuda")
+        rows = x[first + count * step:first + count * step + m]
+        q, s = torch.empty((m, k), dtype=torch.int8, device="cuda"), torch.empty((m, -(-k // 128)), dtype=torch.float32, device="cuda")
+        assert lib.wq8_quantize_blocks_at(x.data_ptr(), q.data_ptr(), s.data_ptr(), m, k, x.stride(0), 1, 0, acts[act], wq._ptr(w), 1e-6, None,
+                                          counter.data_ptr(), first, step, stream) == 0
+        q_plain, s_plain = wq.quantize_blocks(rows, 0, act, w, 1e-6)
+        assert torch.equal(q, q_plain) and torch.equal(s, s_plain)
+        hi, lo, rs = (torch.empty((m, k), dtype=torch.int8, device="cuda"), torch.empty((m, k), dtype=torch.int8, device="cuda"),
+                      torch.empty(m, dtype=torch.float32, device="cuda"))
+        assert lib.wq8_quantize_at(x.data_ptr(), hi.data_ptr(), lo.data_ptr(), rs.data_ptr(), m, k, x.stride(0), 1, 0, acts[act], wq._ptr(w), 1e-6,
+                                   counter.data_ptr(), first, step, stream) == 0
+        hi_plain, lo_plain, rs_plain = wq.quantize(rows, 0, True, act, w, 1e-6)
+        assert torch.equal(hi, hi_plain) and torch.equal(lo, lo_plain) and torch.equal(rs, rs_plain)
+    # no counter: row 0, whatever first and step say
+    q, s = torch.empty((m, k), dtype=torch.int8, device="cuda"), torch.empty((m, -(-k // 128)), dtype=torch.float32, device="cuda")
+    assert lib.wq8_quantize_blocks_at(x.data_ptr(), q.data_ptr(), s.data_ptr(), m, k, x.stride(0), 1, 0, acts[act], wq._ptr(w), 1e-6, None, None, 7, 9,
+                                      stream) == 0
+    q_plain, s_plain = wq.quantize_blocks(x[:m], 0, act, w, 1e-6)
+    assert torch.equal(q, q_plain) and torch.equal(s, s_plain)

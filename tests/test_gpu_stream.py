@@ -101,3 +101,30 @@ def test_planes_keep_small_values_next_to_large_ones(wq):
     expected = (x.double() @ w.double().T * 0.001).to(torch.bfloat16)
     assert rel(y, expected) < 2e-3
     assert wq.debug_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+@pytest.mark.parametrize("tokens", [1, 4, 8])
+@pytest.mark.parametrize("shape", [(28672, 4096), (4096, 14336)], ids=["up", "down"])
+def test_planes_with_an_outlier_in_every_run(wq, shape, tokens, dtype):
+    """The worst case of the digit-plane kernel: every run of 128 activations holds one value 2^10 times larger than the rest and all
+    weights are live, so the small values carry the fewest digits.  Bar: 1e-3 against the reference's own CUDA kernels, which multiply
+    the unrewritten activations; and the planes must actually be the kernel that ran."""
+    n, k = shape
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(tokens, k, generator=g)
+    x[:, 5::128] *= 1024.0
+    x = x.to(dtype)
+    w = rand_int8((n, k), 78)
+    sw = torch.rand(n, generator=g) * 0.002 + 0.0001
+    bias = randn((n,), dtype, 79)
+    gx, gw, gsw, gbias = cuda(x, w, sw, bias)
+    assert wq._require().wq8_stream_planes_workspace(tokens, n, k, 148) > 0
+    for entry, reference in ((wq.gemv_lines, reflib.gemv_lines), (wq.small, reflib.small)):
+        if entry is wq.gemv_lines and tokens > 4:
+            continue
+        y = entry(gx, gw, gsw, gbias)
+        assert rel(y, reference(gx, gw, gsw, gbias)) < 1e-3
+        exact = (x.double() @ (w.double() * sw.double()[:, None]).T + bias.double())
+        assert rel(y, exact.float()) < 4e-3  # the output's own rounding to 8 or 11 bits
+    assert wq.debug_status() == 0

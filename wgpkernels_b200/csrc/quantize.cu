@@ -14,7 +14,7 @@ template <class T> WQ_DEVICE const T* first_row(const T* x, int64_t ldx, const R
 }
 
 // ---- one 256-element chunk -> two 128-element blocks (16 lanes each): absmax, scale, INT8 codes --------------------------
-template <int GROUP>
+template <int GROUP, bool PAIRS = false>
 WQ_DEVICE void store_chunk_as_blocks(const float* v, int lane, int64_t row, int base, int k, int kblocks, int8_t* __restrict__ q,
                                      float* __restrict__ scale) {
     float amax = 0.f;
@@ -33,43 +33,20 @@ WQ_DEVICE void store_chunk_as_blocks(const float* v, int lane, int64_t row, int 
     const int col = base + lane * 8;
     if (col < k) {
         int c[8];
+        if constexpr (PAIRS) {  // two-wide multiplies (each half rounds as the scalar multiply does): fewer instructions where the input
+                                // operation leaves registers to pair; the row kernels, short of registers, keep the scalar form
+            const float2 inverse = make_float2(inv, inv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) c[j] = __float2int_rn(v[j] * inv);
-        *reinterpret_cast<uint2*>(q + row * k + col) = make_uint2(pack_bytes(c[0], c[1], c[2], c[3]), pack_bytes(c[4], c[5], c[6], c[7]));
-    }
-}
-
-// Blocks are independent when no row statistic is needed: a warp per 256-element chunk, persistent warps, two chunks in flight per warp.
-template <class T, int GROUP, int ACT>
-__global__ void __launch_bounds__(256) quantize_blocks_stream(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, int m,
-                                                              int k, int64_t ldx, RowShift shift) {
-    x = first_row(x, ldx, shift);
-    const int lane = threadIdx.x & 31;
-    const int chunks = (k + kChunk - 1) / kChunk, kblocks = (k + kBlockK - 1) / kBlockK;
-    const int64_t items = int64_t(m) * chunks, warps = int64_t(gridDim.x) * 8, warp_id = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    // each warp takes a contiguous run of (row, chunk) items: one division up front, then the chunk index just advances
-    const int64_t per_warp = (items + warps - 1) / warps, first = warp_id * per_warp;
-    const int64_t last = first + per_warp < items ? first + per_warp : items;
-    if (first >= last) return;
-    int64_t row = first / chunks;
-    int chunk = int(first - row * chunks);
-    for (int64_t item = first; item < last; item += 2) {
-        const bool pair = item + 1 < last;
-        const int64_t row0 = row;
-        const int base0 = chunk * kChunk;
-        if (++chunk == chunks) { chunk = 0; ++row; }
-        const int64_t row1 = row;
-        const int base1 = chunk * kChunk;
-        if (pair && ++chunk == chunks) { chunk = 0; ++row; }
-        float v0[8], v1[8];
-        load_op<T, ACT>(x + row0 * ldx, k, base0 + lane * 8, v0, base0 + lane * 8 < k);
-        load_op<T, ACT>(x + row1 * ldx, k, base1 + lane * 8, v1, pair && base1 + lane * 8 < k);
-        rotate_chunk<GROUP>(v0);
-        store_chunk_as_blocks<GROUP>(v0, lane, row0, base0, k, kblocks, q, scale);
-        if (pair) {  // warp-uniform
-            rotate_chunk<GROUP>(v1);
-            store_chunk_as_blocks<GROUP>(v1, lane, row1, base1, k, kblocks, q, scale);
+            for (int j = 0; j < 8; j += 2) {
+                const float2 scaled = __fmul2_rn(make_float2(v[j], v[j + 1]), inverse);
+                c[j] = __float2int_rn(scaled.x);
+                c[j + 1] = __float2int_rn(scaled.y);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) c[j] = __float2int_rn(v[j] * inv);
         }
+        *reinterpret_cast<uint2*>(q + row * k + col) = make_uint2(pack_bytes(c[0], c[1], c[2], c[3]), pack_bytes(c[4], c[5], c[6], c[7]));
     }
 }
 
@@ -134,6 +111,24 @@ __global__ void __launch_bounds__(kRowThreads) quantize_blocks_rms(const T* __re
             store_chunk_as_blocks<GROUP>(v, lane, row, base, k, kblocks, q, scale);
         }
     }
+}
+
+// No row statistic: every (row, 256-element chunk) is independent.  One warp per item and nothing else: the row is the grid's y
+// coordinate and the chunk comes from x, so there is no loop, no division and no bookkeeping -- the input operations (the accurate
+// tanhf / expf of gelu and swiglu) are what these launches spend their time on, and every register and instruction beside them
+// costs occupancy.  The host launches batches of at most 65535 rows (the grid's y limit).
+template <class T, int GROUP, int ACT>
+__global__ void __launch_bounds__(256) quantize_blocks_items(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, int64_t row0, int k,
+                                                             int64_t ldx, RowShift shift) {
+    const int lane = threadIdx.x & 31;
+    const int base = (blockIdx.x * 8 + (threadIdx.x >> 5)) * kChunk;
+    if (base >= k) return;
+    const int kblocks = (k + kBlockK - 1) / kBlockK;
+    const int64_t row = row0 + blockIdx.y;
+    float v[8];
+    load_op<T, ACT>(first_row(x, ldx, shift) + row * ldx, k, base + lane * 8, v, base + lane * 8 < k);
+    rotate_chunk<GROUP>(v);
+    store_chunk_as_blocks<GROUP, true>(v, lane, row, base, k, kblocks, q, scale);
 }
 
 // ---- row-wise INT8 (one scale per row), optional exact hi / lo split -----------------------------------------------------
@@ -311,8 +306,11 @@ static int launch_blocks(const void* x, int8_t* q, float* scale, int m, int k, i
         else if (k <= 16384) quantize_blocks_rms<T, GROUP, 8><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
         else quantize_blocks_rms<T, GROUP, 0><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
     } else {
-        const int64_t items = int64_t(m) * ((k + kChunk - 1) / kChunk);
-        quantize_blocks_stream<T, GROUP, ACT><<<persistent_ctas((items + 1) / 2), 256, 0, stream>>>(src, q, scale, m, k, ldx, shift);
+        const int chunks = (k + kChunk - 1) / kChunk;
+        for (int64_t row0 = 0; row0 < m; row0 += 65535) {
+            const dim3 grid((chunks + 7) / 8, unsigned(m - row0 < 65535 ? m - row0 : 65535));
+            quantize_blocks_items<T, GROUP, ACT><<<grid, 256, 0, stream>>>(src, q, scale, row0, k, ldx, shift);
+        }
     }
     return int(cudaGetLastError());
 }

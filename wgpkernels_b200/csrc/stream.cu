@@ -441,8 +441,8 @@ __global__ void __launch_bounds__(kBulkThreads, 1) stream_bulk(const __grid_cons
 // stream_bulk spends most of its instructions turning weight bytes into BF16 / FP16 (8 instructions per 4 bytes): at 1-8 tokens that,
 // not the HBM, bounds it.  Here the few activations are rewritten instead, once per call by split_planes: every run of 128 values of a
 // token becomes three planes of signed 7-bit digits with one power of two, x = 2^(E-7) (q0 + q1 / 128 + q2 / 16384), exact for every
-// value within 2^14 of the largest of its run (a BF16 / FP16 value has at most 11 significant bits; smaller values are truncated below
-// 2^-21 of the run's largest).  The weights then go into mma.sync.m16n8k32.s8 untouched: per plane an exact INT32 dot product over the
+// value within 2^14 of the largest of its run (a BF16 / FP16 value has at most 11 significant bits; smaller values are rounded to the
+// nearest multiple of 2^-21 of the run's power of two: an absolute error of at most 2^-21 of the run's largest value).  The weights then go into mma.sync.m16n8k32.s8 untouched: per plane an exact INT32 dot product over the
 // run, combined and scaled in FP32.  Same rings, reducer and hand-overs as stream_bulk.
 // ---------------------------------------------------------------------------------------------------------------------
 constexpr int kPlaneRun = 128;   // values sharing one power of two
@@ -465,7 +465,9 @@ __global__ void __launch_bounds__(256) split_planes(const T* __restrict__ x, int
     float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
-    // amax < 2^E; the digits of v / 2^E in base 128, truncating toward zero (every remainder keeps the sign and is exact in FP32)
+    // amax < 2^E; the digits of v / 2^E in base 128: the first two truncate toward zero (every remainder keeps the sign and is exact in
+    // FP32), the last one rounds to nearest, so the rewritten value is within 2^(E-22) of v -- half a unit of the last digit, and no
+    // bias toward zero; a value within 2^14 of the run's largest (BF16) has no bits below the last digit and is exact
     int exponent = 0;
     if (amax > 0.f) frexpf(amax, &exponent);
     exponent = max(exponent, -110);  // 2^(7 - E) and 2^(E - 7) stay finite, normal numbers; runs of denormal-sized values become zeros
@@ -476,7 +478,7 @@ __global__ void __launch_bounds__(256) split_planes(const T* __restrict__ x, int
         float f = v[j] * down;  // |f| < 128
 #pragma unroll
         for (int p = 0; p < 3; ++p) {
-            const float digit = truncf(f);
+            const float digit = p < 2 ? truncf(f) : fminf(fmaxf(rintf(f), -127.f), 127.f);
             packed[p] |= (uint32_t(int(digit)) & 0xffu) << (8 * j);
             f = (f - digit) * 128.f;
         }
@@ -883,7 +885,8 @@ WQ_API int64_t wq8_stream_planes_workspace(int m, int n, int k, int sms) {
 
 // Weight-only INT8 linear for at most 8 tokens with the activations split into INT8 digit planes (see stream_planes): the weights go into
 // INT8 tensor-core MMAs as they are.  workspace: wq8_stream_planes_workspace() bytes, 16-byte aligned.  Values: FP32 sums of exact
-// INT32 dot products per 128 values of K; an activation more than 2^14 times smaller than the largest of its 128 is truncated.
+// INT32 dot products per 128 values of K; an activation more than 2^14 times smaller than the largest of its 128 is rounded to the
+// nearest 2^-21 of that largest value's power of two (relative error of the whole product below 2^-21 per run).
 WQ_API int wq8_stream_planes(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
                              void* y, int m, int n, int k, int dtype, int sms, void* workspace, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;

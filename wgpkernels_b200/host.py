@@ -69,3 +69,70 @@ class HostLinear:
             if event is not None:
                 compute.wait_event(event)  # the caller's stream sees the call as complete once every chunk is back on the host
         return out_host
+
+
+def _shared_pinned(path, shape, dtype, create):
+    """A host tensor backed by a file of shared memory that every process of the node maps, registered with CUDA so that copies to
+    and from it are asynchronous (the same bytes in all processes: the ranks of a node fill and read one activation together)."""
+    count = 1
+    for extent in shape:
+        count *= extent
+    size = count * torch.empty((), dtype=dtype).element_size()
+    if create:
+        with open(path, "wb") as handle:
+            handle.truncate(size)
+    tensor = torch.from_file(path, shared=True, size=count, dtype=dtype).view(shape)
+    code = torch.cuda.cudart().cudaHostRegister(tensor.data_ptr(), size, 0)
+    if int(code) != 0:
+        raise RuntimeError(f"cudaHostRegister failed ({code})")
+    return tensor
+
+
+class ShardedHostLinear:
+    """The host-memory linear on all GPUs of a node: one process per GPU (torch.distributed initialised), the activation `x` (rows, K)
+    and the output `y` (rows, N) live in host memory shared by the processes, and rank r moves and multiplies rows
+    [r rows / g, (r + 1) rows / g) only, with the whole weight on every GPU (79 MB for the fused QKV projection: replicating it is
+    cheap, moving activations between GPUs is not).  Every GPU has its own PCIe link, so the copies of the g bands run side by side:
+    no bytes cross NVLink and no collective is involved.  Each band runs through HostLinear's three-stream pipeline.
+
+    x and y are attributes: fill x (any rank; they are the same bytes), call the object on every rank, synchronize and barrier, read y."""
+
+    def __init__(self, weight, scale, bias=None, rows=0, k=0, dtype=torch.bfloat16, chunk_rows=4096, group=None, tag="0"):
+        import torch.distributed as dist
+        self.group = group
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.rank, self.world = rank, world
+        per_rank = -(-rows // world)
+        self.start, self.stop = min(rank * per_rank, rows), min((rank + 1) * per_rank, rows)
+        self._paths = [f"/dev/shm/wgpkernels_b200_{tag}_{name}" for name in ("x", "y")]
+        shapes = ((rows, k), (rows, weight.shape[0]))
+        if rank == 0:
+            self.x, self.y = (_shared_pinned(path, shape, dtype, True) for path, shape in zip(self._paths, shapes))
+        if world > 1:
+            dist.barrier(group)
+        if rank != 0:
+            self.x, self.y = (_shared_pinned(path, shape, dtype, False) for path, shape in zip(self._paths, shapes))
+        self.inner = HostLinear(weight, scale, bias, chunk_rows=chunk_rows)
+        self.h2d_bytes = self.x.numel() * self.x.element_size()
+        self.d2h_bytes = self.y.numel() * self.y.element_size()
+
+    def __call__(self, **kwargs):
+        if self.stop > self.start:
+            self.inner(self.x[self.start:self.stop], self.y[self.start:self.stop], **kwargs)
+        return self.y
+
+    def close(self):
+        import os
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        for tensor in (self.x, self.y):
+            torch.cuda.cudart().cudaHostUnregister(tensor.data_ptr())
+        if self.world > 1:
+            dist.barrier(self.group)
+        if self.rank == 0:
+            for path in self._paths:
+                try:
+                    os.unlink(path)
+                except OSError:
+                    pass
