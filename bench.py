@@ -510,14 +510,20 @@ def main():
         dist.all_reduce(mismatches)
         parity = {"rows": band.stop - band.start, "columns": n_total, "ranks": world, "mismatches": int(mismatches.item()),
                   "what": "every rank: its gathered (M, N) output on this band of rows against the unsharded linear computed on that rank, element for element"}
-        consumer_ms = timed(lambda: layer(g.x, gather=None, residual=local_residual, residual_scale=local_rscale, **common), args.steps)
+        consumer_step = lambda: layer(g.x, gather=None, residual=local_residual, residual_scale=local_rscale, **common)
+        for _ in range(2):
+            consumer_step()  # the tile tuner runs on the first call of a shape: outside the timed region
+        consumer_ms = timed(consumer_step, args.steps)
         sharded_consumer = {"ms_per_step": consumer_ms / args.steps, "value": ops * args.steps / (consumer_ms * 1e-3) / 1e12, "unit": UNIT,
                             "what": "output kept column-sharded (M, N / g) on each rank, no exchange: the form a consumer sharded the same way reads "
                                     "(attention heads of a fused q / k / v projection)"}
         per_rank = -(-m // world)
         rows = slice(min(rank * per_rank, m), min((rank + 1) * per_rank, m))
         token_residual = None if g.residual is None else g.residual[rows]
-        token_ms = timed(lambda: wq.linear(g.x[rows], g.weight, g.scale, g.bias, residual=token_residual, residual_scale=g.residual_scale, **common), args.steps)
+        token_step = lambda: wq.linear(g.x[rows], g.weight, g.scale, g.bias, residual=token_residual, residual_scale=g.residual_scale, **common)
+        for _ in range(2):
+            token_step()
+        token_ms = timed(token_step, args.steps)
         token_sharded = {"ms_per_step": token_ms / args.steps, "value": ops * args.steps / (token_ms * 1e-3) / 1e12, "unit": UNIT,
                          "what": "rows sharded (M / g tokens per rank), weight replicated, full-width output rows on their rank, no exchange"}
 

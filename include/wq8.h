@@ -104,8 +104,10 @@ int wq8_gemm_at(const int8_t* a, const int8_t* a_lo, const float* sa, const int8
 
 /* Weight-only INT8 for at most 32 unquantized tokens: Y = X @ (W * sw).T + bias (+ residual), FP32
  * accumulation of exact products.  K multiple of 64; x and w 16-byte aligned, ldx a multiple of 8 (-2 otherwise).
- * slots / counters: sizes from wq8_small_workspace(); counters zero on entry, left zero.
- * Replaces int8_gemm.cu:1752-1759 and :1693-1697. */
+ * slots / counters: scratch of the sizes wq8_small_workspace() reports (slots 256-byte aligned); counters zero on entry,
+ * left zero.  With scratch and K a multiple of 128 the linear runs on tcgen05 (the activations as INT8 digit planes --
+ * see wq8_stream_planes for their accuracy --, K ranges shared over all SMs, partial sums added in a fixed order);
+ * without scratch (NULL) on the kernels that need none.  Replaces int8_gemm.cu:1752-1759 and :1693-1697. */
 int wq8_small(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
               void* y, int m, int n, int k, int dtype, int sms, float* slots, int* counters, wq8_stream_t stream);
 void wq8_small_workspace(int m, int n, int k, int sms, int64_t* sizes);
@@ -151,7 +153,7 @@ int wq8_stream_planes(const void* x, int64_t ldx, const int8_t* w, const float* 
 /* wq8_small for callers that cannot allocate device memory (no counterpart in the reference, which always takes caller scratch).
  * A host that reaches this library through a bare FFI with buffers it was handed, a serving loop under a fixed memory budget, code
  * running during CUDA graph capture or in a section where cudaMalloc is not allowed: none of them can supply the K-split scratch
- * wq8_small asks for.  Here the scratch is a static device buffer inside the library (2 MiB + 4 KiB per GPU that loads it, held until
+ * wq8_small asks for.  Here the scratch is a static device buffer inside the library (8 MiB + 4 KiB per GPU that loads it, held until
  * the process exits); nothing is allocated or freed.  The first call on a device looks up the buffer's device address and should come
  * before any stream capture.  Same arguments and error codes as wq8_small without `slots` / `counters`, the same kernel choice and so
  * the same values bit for bit; -5 when the shape's scratch exceeds the buffer.  All calls on a device share the buffer: calls whose

@@ -91,11 +91,18 @@ def test_workspace_queries(lib):
     sizes = (ctypes.c_int64 * 2)()
     lib.wq8_gemm_workspace(32760, 15360, 5120, 10, 148, 1, sizes)
     assert sizes[0] >= 0 and sizes[1] >= 0 and sizes[1] <= 4096
-    # few tokens, few channels: K is split across CTAs and the partial sums need slots and one counter per tile
+    # K a multiple of 128: the tensor-core kernel -- digit planes (96 rows for 9-32 token slots... 48 for 16), their powers of two and two
+    # pieces of partial sums per CTA, each rounded up to 256 bytes; one counter per tile of 128 output channels
     lib.wq8_small_workspace(16, 1024, 14336, 148, sizes)
-    assert sizes[0] > 0 and 0 < sizes[1] <= 4096
-    # many channels: every SM streams without splitting
+    assert sizes[0] == 48 * 14336 + (14336 // 128) * 16 * 4 + 148 * 2 * 128 * 16 * 4 and sizes[1] == 4 * 8
     lib.wq8_small_workspace(16, 28672, 4096, 148, sizes)
+    assert sizes[0] == 48 * 4096 + (4096 // 128) * 16 * 4 + 148 * 2 * 128 * 16 * 4 and sizes[1] == 4 * 224
+    lib.wq8_small_workspace(3, 256, 256, 148, sizes)  # fewer (tile, K block) pairs than SMs: one CTA per pair
+    assert sizes[0] == 32 * 256 + 256 + 4 * 2 * 128 * 8 * 4 and sizes[1] == 8
+    # K not a multiple of 128: the direct-load kernel; few channels split K across CTAs, many do not
+    lib.wq8_small_workspace(16, 1024, 14336 + 64, 148, sizes)
+    assert sizes[0] > 0 and 0 < sizes[1] <= 4096
+    lib.wq8_small_workspace(16, 28672, 4096 + 64, 148, sizes)
     assert sizes[0] == 0 and sizes[1] == 0
 
 

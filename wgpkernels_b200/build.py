@@ -16,7 +16,7 @@ from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 PACKAGE = Path(__file__).resolve().parent
-SOURCES = ("api.cu", "quantize.cu", "stream.cu", "gemm_tc.cu")
+SOURCES = ("api.cu", "quantize.cu", "stream.cu", "stream_tc.cu", "gemm_tc.cu")
 PROBE_SOURCES = ("probe.cu",)
 HEADERS = ("common.cuh", "tc_ptx.cuh")
 ARCH_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a")

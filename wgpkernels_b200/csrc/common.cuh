@@ -197,6 +197,12 @@ template <int GROUP> __host__ __device__ constexpr float group_norm() { return G
 // swizzle, zero fill outside; false when the driver entry point is missing or refuses the description.
 bool make_byte_matrix_map(CUtensorMap* map, const void* base, int rows, int row_bytes, int box_bytes, int box_rows);
 int stream_status_take();  // stream.cu: status of the weight-streaming kernels on the current device (0 = fine), cleared by the call
+// stream_tc.cu: the few-token linear on tcgen05 (digit planes): scratch bytes of a shape (0: not this kernel's shape; *counter_bytes: its
+// tile counters), the launch (x already transformed; workspace and zeroed counters of those sizes), and its status word
+int64_t stream_tc_workspace(int m, int n, int k, int sms, int64_t* counter_bytes);
+int stream_tc_launch(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale, void* y, int m,
+                     int n, int k, int dtype, int sms, void* workspace, int* counters, cudaStream_t stream);
+int stream_tc_status_take();
 
 enum Status : int { kOk = 0, kTimeoutFull = 1, kTimeoutEmpty = 2, kTimeoutTmemFull = 3, kTimeoutTmemEmpty = 4, kTimeoutScales = 5, kTimeoutParams = 6, kStatusSharedAlignment = 7 };
 

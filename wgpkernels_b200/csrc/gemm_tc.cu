@@ -733,6 +733,9 @@ __global__ void regroup_weight_scales(const float* __restrict__ sb, float* __res
     }
 }
 
+// The same map for other translation units (the few-token tensor-core kernel): (rows, k) bytes, boxes of box_rows x 128 bytes, 128-byte swizzle.
+bool make_swizzled_byte_map(CUtensorMap* map, const void* base, int64_t rows, int k, int box_rows) { return make_map(map, base, rows, k, box_rows); }
+
 constexpr int kScalePad = 256;
 static int padded_n(int n) { return (n + kScalePad - 1) / kScalePad * kScalePad; }
 

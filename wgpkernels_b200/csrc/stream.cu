@@ -1,17 +1,16 @@
-// Few-token paths ('lines': 1-4 tokens, 'small': up to 32 tokens): weight-only INT8.  The activations stay unquantized; the INT8
-// weight matrix is streamed once from HBM with 128-bit loads, converted exactly to BF16 / FP16 in registers and multiplied on tensor
-// cores with FP32 accumulation.  HBM-bound: the design goal is bytes in flight (every SM streaming, 4 x 1 KiB per warp outstanding)
-// and a fixed-order (deterministic) reduction.  Replaces w8a16_small / gemv_lines of the reference (wgpkernels/int8/int8_gemm.cu:
-// 1039-1151, 1772-1810): same values up to FP32 summation order.
+// Few-token paths ('lines': 1-4 tokens, 'small': up to 32 tokens): weight-only INT8.  The activations stay unquantized (or are rewritten
+// exactly as digit planes); the INT8 weight matrix is streamed once from HBM.  HBM-bound: the design goal is bytes in flight on every
+// SM and fixed-order (deterministic) reductions.  Kernels of this file:
+//   stream_bulk    up to 16 tokens, no scratch: weights through per-warp TMA rings, converted exactly to BF16 / FP16 in registers for
+//                  mma.sync.m16n8k16 (what wq8_gemv_lines runs, and wq8_small without scratch)
+//   stream_planes  up to 8 tokens: the activations as INT8 digit planes, the weights into mma.sync.m16n8k32.s8 untouched
+//   direct_rows    every other shape and alignment, on plain CUDA cores, with an optional split of K over CTAs
+// and stream_tc.cu holds the tcgen05 kernel that wq8_small runs with its caller's scratch (up to 32 tokens).
+// Together they replace w8a16_small / gemv_lines of the reference (wgpkernels/int8/int8_gemm.cu:1039-1151, 1772-1810): same values up
+// to FP32 summation order.
 #include "common.cuh"
 
 namespace wq {
-
-WQ_DEVICE uint4 load_streaming(const void* p) {
-    uint4 r;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
-    return r;
-}
 
 WQ_DEVICE uint32_t byte_permute(uint32_t a, uint32_t b, uint32_t selector) {
     uint32_t d;
@@ -54,93 +53,62 @@ template <> WQ_DEVICE void mma_16x8x16<__half>(float* d, uint32_t a0, uint32_t a
 }
 
 constexpr int kStreamChunk = 64;   // elements of K one warp step covers: 16 contiguous bytes per lane of each of its two rows
-constexpr int kStreamUnroll = 4;   // chunks in flight per warp
 
-// Output channels are the MMA rows ("swap AB"): a warp owns 16 channels, lane (g = lane / 4, t = lane % 4) streams 16 contiguous bytes of
-// rows g and g + 8 per chunk.  Any permutation of K applied to both operands leaves the product unchanged, so the bytes are used where they
-// land: MMA q of a chunk takes bytes 4q..4q+3 of both rows (logical k 2t, 2t+1 | 2t+8, 2t+9) and the tokens' values at the same positions.
-// The 8 warps of a CTA are wn channel blocks x wk slices of K (wn * wk = 8): many channels -> no reduction in the CTA, few channels -> the
-// CTA splits K so that every SM streams.  gridDim.y splits K further across CTAs (partials through `slots`, last arriver reduces in order).
-template <class T, int MT>
-__global__ void __launch_bounds__(256) stream_mma(const T* __restrict__ x, int64_t ldx, const int8_t* __restrict__ w, const float* __restrict__ sw,
-                                                  const T* __restrict__ bias, const T* residual, const T* __restrict__ rscale, T* y, int m, int n, int k,
-                                                  int wk, float* __restrict__ slots, int* __restrict__ counters) {
-    __shared__ float partial[8][MT * 8][17];
+// ---------------------------------------------------------------------------------------------------------------------
+// direct_rows: the shapes and alignments the tensor-core kernels do not take (K any multiple of 4, weights 4-byte aligned, activation
+// rows 8-byte aligned, up to 32 tokens), and the K-split path of callers that bring scratch.  Plain CUDA cores, one THREAD per output
+// channel: a CTA owns 32 channels (the lanes) and its 8 warps share the CTA's range of K; a thread walks its channel's row four weight
+// bytes at a time (exact INT8 -> FP32), multiplying them with the tokens' activations, which every lane of the warp reads from the
+// same address (one broadcast transaction).  The 8 warps' sums meet in shared memory and are added in warp order; with gridDim.y > 1
+// the CTAs of a channel block split K further, each writes its sums to a slot of the caller's scratch and the last one to arrive
+// (a counter per channel block, zero on entry, left zero) adds the slots in split order: every addition order is fixed.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int kDirectChannels = 32, kDirectWarps = 8;
+
+template <class T, int TOKENS>
+__global__ void __launch_bounds__(32 * kDirectWarps) direct_rows(const T* __restrict__ x, int64_t ldx, const int8_t* __restrict__ w, const float* __restrict__ sw,
+                                                                  const T* __restrict__ bias, const T* residual, const T* __restrict__ rscale, T* y, int m, int n,
+                                                                  int k, float* __restrict__ slots, int* __restrict__ counters) {
+    __shared__ float partial[kDirectWarps][TOKENS][kDirectChannels + 1];
     __shared__ int is_last;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int wn = 8 / wk, slice = warp % wk, channel_block = warp / wk;
-    const int ch0 = (blockIdx.x * wn + channel_block) * 16 + g, ch1 = ch0 + 8;
-    const bool ok0 = ch0 < n, ok1 = ch1 < n;
-    const int chunks = k / kStreamChunk, splits = gridDim.y;
-    const int c_begin = int(int64_t(blockIdx.y) * chunks / splits), c_end = int(int64_t(blockIdx.y + 1) * chunks / splits);
-    const int8_t* w0 = w + int64_t(ok0 ? ch0 : 0) * k + 16 * t;
-    const int8_t* w1 = w + int64_t(ok1 ? ch1 : 0) * k + 16 * t;
-    const T* x_row[MT];
-    bool x_ok[MT];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int channel = blockIdx.x * kDirectChannels + lane;
+    const int quads = k / 4, splits = gridDim.y;
+    // this CTA's quads of K, then this warp's share of them
+    const int cta_begin = int(int64_t(blockIdx.y) * quads / splits), cta_end = int(int64_t(blockIdx.y + 1) * quads / splits);
+    const int begin = cta_begin + int(int64_t(warp) * (cta_end - cta_begin) / kDirectWarps);
+    const int end = cta_begin + int(int64_t(warp + 1) * (cta_end - cta_begin) / kDirectWarps);
+    const uint32_t* row = reinterpret_cast<const uint32_t*>(w + int64_t(channel < n ? channel : 0) * k);
+    float acc[TOKENS];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        const int token = mt * 8 + g;
-        x_ok[mt] = token < m;
-        x_row[mt] = x + int64_t(x_ok[mt] ? token : 0) * ldx + 16 * t;
-    }
-    float acc[MT][4];
+    for (int t = 0; t < TOKENS; ++t) acc[t] = 0.f;
+    for (int quad = begin; quad < end; ++quad) {
+        const uint32_t packed = __ldg(row + quad);
+        const float w0 = float(int(int8_t(packed))), w1 = float(int(int8_t(packed >> 8))), w2 = float(int(int8_t(packed >> 16))), w3 = float(int(packed) >> 24);
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
-
-    for (int c = c_begin + slice; c < c_end; c += wk * kStreamUnroll) {
-        uint4 row0[kStreamUnroll], row1[kStreamUnroll];
-#pragma unroll
-        for (int u = 0; u < kStreamUnroll; ++u) {
-            const int cc = c + wk * u;
-            const bool inside = cc < c_end;
-            row0[u] = inside && ok0 ? load_streaming(w0 + int64_t(cc) * kStreamChunk) : make_uint4(0u, 0u, 0u, 0u);
-            row1[u] = inside && ok1 ? load_streaming(w1 + int64_t(cc) * kStreamChunk) : make_uint4(0u, 0u, 0u, 0u);
-        }
-#pragma unroll
-        for (int u = 0; u < kStreamUnroll; ++u) {
-            const int cc = c + wk * u;
-            const bool inside = cc < c_end;  // chunks past the range carry zero weights: no divergent exit inside the unrolled body
-            uint4 xv[MT][2];
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                const T* p = x_row[mt] + int64_t(cc) * kStreamChunk;
-                xv[mt][0] = x_ok[mt] && inside ? __ldg(reinterpret_cast<const uint4*>(p)) : make_uint4(0u, 0u, 0u, 0u);
-                xv[mt][1] = x_ok[mt] && inside ? __ldg(reinterpret_cast<const uint4*>(p) + 1) : make_uint4(0u, 0u, 0u, 0u);
-            }
-            const uint32_t* r0 = reinterpret_cast<const uint32_t*>(&row0[u]);
-            const uint32_t* r1 = reinterpret_cast<const uint32_t*>(&row1[u]);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                uint32_t a0, a1, a2, a3;
-                int8x4_to_pairs<T>(r0[q], a0, a2);
-                int8x4_to_pairs<T>(r1[q], a1, a3);
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    const uint32_t* xs = reinterpret_cast<const uint32_t*>(&xv[mt][q >> 1]);
-                    mma_16x8x16<T>(acc[mt], a0, a1, a2, a3, xs[(q & 1) * 2], xs[(q & 1) * 2 + 1]);
-                }
+        for (int t = 0; t < TOKENS; ++t) {
+            if (t < m) {  // uniform
+                const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + int64_t(t) * ldx + 4 * quad));
+                float x0, x1, x2, x3;
+                unpack_pair<T>(raw.x, x0, x1);
+                unpack_pair<T>(raw.y, x2, x3);
+                acc[t] = fmaf(w3, x3, fmaf(w2, x2, fmaf(w1, x1, fmaf(w0, x0, acc[t]))));
             }
         }
     }
-    // acc[mt] = {(channel g, token 2t), (g, 2t + 1), (g + 8, 2t), (g + 8, 2t + 1)} of token block mt
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        partial[warp][mt * 8 + 2 * t][g] = acc[mt][0];
-        partial[warp][mt * 8 + 2 * t + 1][g] = acc[mt][1];
-        partial[warp][mt * 8 + 2 * t][g + 8] = acc[mt][2];
-        partial[warp][mt * 8 + 2 * t + 1][g + 8] = acc[mt][3];
-    }
+    for (int t = 0; t < TOKENS; ++t) partial[warp][t][lane] = acc[t];
     __syncthreads();
-    constexpr int kPerBlock = MT * 8 * 16;  // outputs of one channel block
-    const int outputs = wn * kPerBlock;
-    float* own = slots ? slots + (int64_t(blockIdx.x) * splits + blockIdx.y) * outputs : nullptr;
-    // the K slices of the CTA, in slice order; the sum lands in the first slice's buffer
-    for (int i = threadIdx.x; i < outputs; i += 256) {
-        const int cb = i / kPerBlock, token = (i % kPerBlock) / 16, c = i % 16;
-        float s = 0.f;
-        for (int ks = 0; ks < wk; ++ks) s += partial[cb * wk + ks][token][c];
-        partial[cb * wk][token][c] = s;
-        if (own) __stcg(own + i, s);
+    // the 8 warps' sums of every (token, channel), in warp order; thread i takes outputs i, i + 256, ...
+    constexpr int kOutputs = TOKENS * kDirectChannels;
+    float* own = slots ? slots + (int64_t(blockIdx.x) * splits + blockIdx.y) * kOutputs : nullptr;
+    for (int i = threadIdx.x; i < kOutputs; i += 32 * kDirectWarps) {
+        const int t = i / kDirectChannels, c = i % kDirectChannels;
+        float sum = partial[0][t][c];
+#pragma unroll
+        for (int part = 1; part < kDirectWarps; ++part) sum += partial[part][t][c];
+        partial[0][t][c] = sum;  // each output is read and written by this thread only
+        if (own) __stcg(own + i, sum);
     }
     if (splits > 1) {
         __threadfence();
@@ -149,22 +117,20 @@ __global__ void __launch_bounds__(256) stream_mma(const T* __restrict__ x, int64
         __syncthreads();
         if (!is_last) return;
         __threadfence();
-        const float* tile = slots + int64_t(blockIdx.x) * splits * outputs;
-        for (int i = threadIdx.x; i < outputs; i += 256) {
-            float s = 0.f;
-            for (int piece = 0; piece < splits; ++piece) s += __ldcg(tile + int64_t(piece) * outputs + i);
-            partial[(i / kPerBlock) * wk][(i % kPerBlock) / 16][i % 16] = s;
+        const float* pieces = slots + int64_t(blockIdx.x) * splits * kOutputs;
+        for (int i = threadIdx.x; i < kOutputs; i += 32 * kDirectWarps) {
+            float sum = 0.f;
+            for (int piece = 0; piece < splits; ++piece) sum += __ldcg(pieces + int64_t(piece) * kOutputs + i);
+            partial[0][i / kDirectChannels][i % kDirectChannels] = sum;
         }
-        if (threadIdx.x == 0) counters[blockIdx.x] = 0;  // left zeroed for the next launch
+        if (threadIdx.x == 0) counters[blockIdx.x] = 0;  // left zero for the next launch
     }
-    __syncthreads();
-    for (int i = threadIdx.x; i < outputs; i += 256) {
-        const int cb = i / kPerBlock, token = (i % kPerBlock) / 16, c = i % 16;
-        const int channel = (blockIdx.x * wn + cb) * 16 + c;
-        if (token < m && channel < n) {
-            float v = partial[cb * wk][token][c] * sw[channel] + (bias ? as_float(bias[channel]) : 0.f);
-            if (residual) v = fmaf(v, rscale ? as_float(rscale[channel]) : 1.f, as_float(residual[int64_t(token) * n + channel]));
-            y[int64_t(token) * n + channel] = round_one<T>(v);
+    for (int i = threadIdx.x; i < kOutputs; i += 32 * kDirectWarps) {
+        const int t = i / kDirectChannels, c = i % kDirectChannels, ch = blockIdx.x * kDirectChannels + c;
+        if (t < m && ch < n) {
+            float v = fmaf(partial[0][t][c], sw[ch], bias ? as_float(bias[ch]) : 0.f);
+            if (residual) v = fmaf(v, rscale ? as_float(rscale[ch]) : 1.f, as_float(residual[int64_t(t) * n + ch]));
+            y[int64_t(t) * n + ch] = round_one<T>(v);
         }
     }
 }
@@ -172,7 +138,7 @@ __global__ void __launch_bounds__(256) stream_mma(const T* __restrict__ x, int64
 // ---------------------------------------------------------------------------------------------------------------------
 // stream_bulk: the same linear with the weights fed by the copy engine.
 //
-// stream_mma keeps at most 4 KiB per warp in flight and only while the warp is not computing; with one or two CTAs per SM that is far
+// A kernel that loads weights straight into registers keeps a few KiB per warp in flight, and only while the warp is not computing: far
 // from the bytes the HBM needs outstanding.  Here every warp owns a ring of kBulkStages stages of 4 KiB in shared memory, filled by
 // the TMA unit (one cp.async.bulk.tensor box of ROWS weight rows x 128 or 256 bytes of K per stage, no multicast, completion counted by
 // an mbarrier per stage; rows past N and bytes past K arrive as zeros): 16 warps x 3 stages x 4 KiB = 192 KiB per SM are requested
@@ -666,104 +632,47 @@ __global__ void __launch_bounds__(kBulkThreads, 1) stream_planes(const __grid_co
     }
 }
 
-// General GEMV for one to four tokens when the tensor-core kernel's alignment does not hold (K multiple of 4 only, rows of x 8-byte
-// aligned): a warp per output channel, four weight bytes per lane and step, exact INT8 -> FP32 conversion, FP32 FMA, butterfly sum.
-template <class T, int ROWS>
-__global__ void __launch_bounds__(256) gemv_cores(const T* __restrict__ x, int64_t ldx, const int8_t* __restrict__ w, const float* __restrict__ sw,
-                                                  const T* __restrict__ bias, const T* residual, const T* __restrict__ rscale, T* y, int n, int k) {
-    const int lane = threadIdx.x & 31, channel = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (channel >= n) return;
-    const int8_t* row = w + int64_t(channel) * k;
-    float acc[ROWS];
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
-#pragma unroll 4
-    for (int base = lane * 4; base < k; base += 128) {
-        const uint32_t packed = __ldg(reinterpret_cast<const uint32_t*>(row + base));
-        float wf[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) wf[j] = float(int(int8_t(packed >> (8 * j))));
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) {
-            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + int64_t(r) * ldx + base));
-            float x0, x1, x2, x3;
-            unpack_pair<T>(raw.x, x0, x1);
-            unpack_pair<T>(raw.y, x2, x3);
-            acc[r] = fmaf(wf[0], x0, acc[r]);
-            acc[r] = fmaf(wf[1], x1, acc[r]);
-            acc[r] = fmaf(wf[2], x2, acc[r]);
-            acc[r] = fmaf(wf[3], x3, acc[r]);
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-        float a = acc[r];
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) a += __shfl_xor_sync(0xffffffffu, a, d);
-        if (lane == 0) {
-            float v = a * sw[channel] + (bias ? as_float(bias[channel]) : 0.f);
-            if (residual) v = fmaf(v, rscale ? as_float(rscale[channel]) : 1.f, as_float(residual[int64_t(r) * n + channel]));
-            y[int64_t(r) * n + channel] = round_one<T>(v);
-        }
-    }
-}
-
 // ---- host side ---------------------------------------------------------------------------------------------------------
-struct StreamPlan { int wk, ctas, splits; };
+struct DirectPlan { int ctas, splits, token_slots; };
 
-// wn channel blocks per CTA: as many as still leave two CTAs per SM; then K splits across CTAs (only with a workspace) until every SM streams,
-// keeping at least four chunks per warp and piece.
-static StreamPlan plan_stream(int n, int k, int sms, bool may_split) {
-    const int blocks = (n + 15) / 16, target = 2 * (sms > 0 ? sms : 148);
-    int wn = 8;
-    while (wn > 1 && (blocks + wn - 1) / wn < target) wn /= 2;
-    StreamPlan p{8 / wn, (blocks + wn - 1) / wn, 1};
-    if (may_split && p.ctas < target) {
-        const int wanted = (target + p.ctas - 1) / p.ctas, most = (k / kStreamChunk) / (p.wk * 4);
+static int tokens_blocks(int m) { return m <= 8 ? 1 : m <= 16 ? 2 : 4; }
+
+// Channel blocks of 32, and as many splits of K across CTAs (only with scratch) as give every SM two CTAs, each split keeping at least
+// 64 quads of K per warp; at most 1024 channel blocks can be split (the counter buffer callers keep).
+static DirectPlan plan_direct(int m, int n, int k, int sms, bool may_split) {
+    DirectPlan p{(n + kDirectChannels - 1) / kDirectChannels, 1, 8 * tokens_blocks(m)};
+    const int target = 2 * (sms > 0 ? sms : 148);
+    if (may_split && p.ctas < target && p.ctas <= 1024) {
+        const int wanted = (target + p.ctas - 1) / p.ctas, most = (k / 4) / (kDirectWarps * 64);
         p.splits = wanted < most ? wanted : (most > 1 ? most : 1);
-        if (p.ctas > 1024) p.splits = 1;  // the caller's counter buffer holds 1024 tiles
     }
     return p;
 }
 
-static int tokens_blocks(int m) { return m <= 8 ? 1 : m <= 16 ? 2 : 4; }
+static int64_t direct_slot_bytes(const DirectPlan& p) { return p.splits > 1 ? int64_t(p.ctas) * p.splits * p.token_slots * kDirectChannels * 4 : 0; }
 
 template <class T>
-static int launch_stream(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
-                         void* y, int m, int n, int k, const StreamPlan& p, float* slots, int* counters, cudaStream_t stream) {
+static int launch_direct(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
+                         void* y, int m, int n, int k, const DirectPlan& p, float* slots, int* counters, cudaStream_t stream) {
     const dim3 grid(p.ctas, p.splits);
     auto xs = static_cast<const T*>(x);
     auto b = static_cast<const T*>(bias), r = static_cast<const T*>(residual), rs = static_cast<const T*>(rscale);
     auto out = static_cast<T*>(y);
     float* sl = p.splits > 1 ? slots : nullptr;
-    switch (tokens_blocks(m)) {
-        case 1: stream_mma<T, 1><<<grid, 256, 0, stream>>>(xs, ldx, w, sw, b, r, rs, out, m, n, k, p.wk, sl, counters); break;
-        case 2: stream_mma<T, 2><<<grid, 256, 0, stream>>>(xs, ldx, w, sw, b, r, rs, out, m, n, k, p.wk, sl, counters); break;
-        default: stream_mma<T, 4><<<grid, 256, 0, stream>>>(xs, ldx, w, sw, b, r, rs, out, m, n, k, p.wk, sl, counters); break;
+    switch (p.token_slots) {
+        case 8: direct_rows<T, 8><<<grid, 32 * kDirectWarps, 0, stream>>>(xs, ldx, w, sw, b, r, rs, out, m, n, k, sl, counters); break;
+        case 16: direct_rows<T, 16><<<grid, 32 * kDirectWarps, 0, stream>>>(xs, ldx, w, sw, b, r, rs, out, m, n, k, sl, counters); break;
+        default: direct_rows<T, 32><<<grid, 32 * kDirectWarps, 0, stream>>>(xs, ldx, w, sw, b, r, rs, out, m, n, k, sl, counters); break;
     }
     return int(cudaGetLastError());
 }
 
-template <class T>
-static int launch_cores(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
-                        void* y, int m, int n, int k, cudaStream_t stream) {
-    auto xs = static_cast<const T*>(x);
-    auto b = static_cast<const T*>(bias), r = static_cast<const T*>(residual), rs = static_cast<const T*>(rscale);
-    auto out = static_cast<T*>(y);
-    const int grid = (n + 7) / 8;
-    if (m == 1) gemv_cores<T, 1><<<grid, 256, 0, stream>>>(xs, ldx, w, sw, b, r, rs, out, n, k);
-    else if (m == 2) gemv_cores<T, 2><<<grid, 256, 0, stream>>>(xs, ldx, w, sw, b, r, rs, out, n, k);
-    else if (m == 3) gemv_cores<T, 3><<<grid, 256, 0, stream>>>(xs, ldx, w, sw, b, r, rs, out, n, k);
-    else gemv_cores<T, 4><<<grid, 256, 0, stream>>>(xs, ldx, w, sw, b, r, rs, out, n, k);
-    return int(cudaGetLastError());
-}
-
-// Rows per work item of stream_bulk / stream_planes (0: the shape is left to stream_mma).  More rows per item read the activations fewer
+// Rows per work item of stream_bulk / stream_planes (0: the shape is left to the other kernels).  More rows per item read the activations fewer
 // times (every item reads all of x from L2), reduce less often and were the faster choice at every measured shape; fewer rows only when
 // the larger items would leave more than a fifth of the SMs' time idle.
 static int plan_bulk(int m, int n, int k, int sms) {
     if (sms <= 0) sms = 148;
-    if (m > 16) return 0;  // 17-32 tokens: four token blocks per lane do not fit the registers of a 17-warp CTA; stream_mma is faster there
+    if (m > 16) return 0;  // 17-32 tokens: four token blocks per lane do not fit the registers of a 17-warp CTA (the tensor-core kernel's job)
     int best = 0;
     double best_balance = 0.0;
     for (int rows = 32; rows >= 8; rows /= 2) {
@@ -862,7 +771,9 @@ int stream_status_take() {
     const int zero = 0;
     if (cudaMemcpyFromSymbol(&code, g_stream_status, sizeof(int)) != cudaSuccess) return -1;
     if (code) cudaMemcpyToSymbol(g_stream_status, &zero, sizeof(int));
-    return code;
+    const int tensor_core_kernel = stream_tc_status_take();
+    if (tensor_core_kernel < 0) return -1;
+    return code ? code : tensor_core_kernel;
 }
 
 static int device_sms() {
@@ -900,10 +811,19 @@ WQ_API int wq8_stream_planes(const void* x, int64_t ldx, const int8_t* w, const 
     return launch_planes<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, workspace, stream);
 }
 
+// The tensor-core kernel takes every shape with K a multiple of 128 and at most 1024 channel tiles (the counter buffer callers keep).
+static int64_t tensor_core_scratch(int m, int n, int k, int sms, int64_t* counter_bytes) {
+    const int64_t bytes = stream_tc_workspace(m, n, k, sms, counter_bytes);
+    return bytes && *counter_bytes <= 4096 ? bytes : 0;
+}
+
 WQ_API void wq8_small_workspace(int m, int n, int k, int sms, int64_t* sizes) {
-    const StreamPlan p = plan_stream(n, k, sms, true);
-    const int64_t outputs = int64_t(8 / p.wk) * tokens_blocks(m) * 8 * 16;
-    sizes[0] = p.splits > 1 ? int64_t(p.ctas) * p.splits * outputs * 4 : 0;
+    if (const int64_t bytes = tensor_core_scratch(m, n, k, sms, &sizes[1])) {
+        sizes[0] = bytes;
+        return;
+    }
+    const DirectPlan p = plan_direct(m, n, k, sms, true);
+    sizes[0] = direct_slot_bytes(p);
     sizes[1] = p.splits > 1 ? 4 * int64_t(p.ctas) : 0;
 }
 
@@ -913,13 +833,16 @@ WQ_API int wq8_small(const void* x, int64_t ldx, const int8_t* w, const float* s
     // every kernel below reads x and w with 16-byte loads (or TMA boxes): unaligned operands are refused, never launched
     if (k <= 0 || k % 64 || m > 32 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -2;
     if (dtype != 0 && dtype != 1) return -1;
+    // with the caller's scratch: the tensor-core kernel (digit planes, stream-K over all SMs)
+    int64_t counter_bytes = 0;
+    if (slots && counters && (reinterpret_cast<uintptr_t>(slots) & 255) == 0 && tensor_core_scratch(m, n, k, sms, &counter_bytes))
+        return stream_tc_launch(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, dtype, sms, slots, counters, stream);
     const int rows = plan_bulk(m, n, k, sms);
     if (rows && dtype == 0) return launch_bulk<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
     if (rows) return launch_bulk<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
-    StreamPlan p = plan_stream(n, k, sms, true);
-    if (p.splits > 1 && (!slots || !counters)) p.splits = 1;
-    if (dtype == 0) return launch_stream<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, slots, counters, stream);
-    return launch_stream<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, slots, counters, stream);
+    const DirectPlan p = plan_direct(m, n, k, sms, slots && counters);
+    if (dtype == 0) return launch_direct<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, slots, counters, stream);
+    return launch_direct<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, slots, counters, stream);
 }
 
 WQ_API int wq8_gemv_lines(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
@@ -932,14 +855,12 @@ WQ_API int wq8_gemv_lines(const void* x, int64_t ldx, const int8_t* w, const flo
         const int sms = device_sms(), rows = plan_bulk(m, n, k, sms);
         if (rows && dtype == 0) return launch_bulk<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
         if (rows) return launch_bulk<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
-        const StreamPlan p = plan_stream(n, k, sms, false);
-        if (dtype == 0) return launch_stream<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, nullptr, nullptr, stream);
-        return launch_stream<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, nullptr, nullptr, stream);
     }
-    // the general kernel reads four weight bytes and four activations (8 bytes) per lane and step
+    // the direct kernel reads four weight bytes and four activations (8 bytes) per step
     if (ldx % 4 || (reinterpret_cast<uintptr_t>(x) & 7) || (reinterpret_cast<uintptr_t>(w) & 3)) return -2;
-    if (dtype == 0) return launch_cores<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, stream);
-    return launch_cores<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, stream);
+    const DirectPlan p = plan_direct(m, n, k, 0, false);
+    if (dtype == 0) return launch_direct<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, nullptr, nullptr, stream);
+    return launch_direct<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, nullptr, nullptr, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -950,7 +871,7 @@ WQ_API int wq8_gemv_lines(const void* x, int64_t ldx, const int8_t* w, const flo
 // with buffers it was given (no allocator of its own on the device), a serving loop that runs under a fixed memory budget and may not
 // grow it per request, code that runs while a CUDA graph is being captured or inside a real-time section where cudaMalloc (which
 // synchronizes and may fail) is off limits.  For them the scratch lives here, in device memory that belongs to the library: every GPU
-// that loads the library holds kStaticScratchBytes (2 MiB + 4 KiB) of it until the process exits.
+// that loads the library holds kStaticScratchBytes (8 MiB + 4 KiB) of it until the process exits.
 //
 // The array's name is only a handle on the host: a kernel must be given the device address, which cudaGetSymbolAddress returns for
 // the device that is current at the time.  It is looked up once per device, on the first call made with that device current -- that
@@ -958,7 +879,7 @@ WQ_API int wq8_gemv_lines(const void* x, int64_t ldx, const int8_t* w, const flo
 // ---------------------------------------------------------------------------------------------------------------------
 namespace wq {
 
-constexpr int64_t kStaticSlotBytes = 2 << 20;     // partial sums: enough for every plan of at most 32 tokens on up to 256 SMs
+constexpr int64_t kStaticSlotBytes = 8 << 20;     // digit planes and partial sums of the tensor-core kernel: 32 tokens, K up to 32768, 148 SMs
 constexpr int64_t kStaticCounterBytes = 4 << 10;  // one counter per tile, at most 1024 tiles
 constexpr int64_t kStaticScratchBytes = kStaticSlotBytes + kStaticCounterBytes;
 static __device__ __align__(256) unsigned char static_scratch[kStaticScratchBytes];
@@ -987,26 +908,30 @@ static unsigned char* static_scratch_address(int* error) {
 }  // namespace wq
 
 // Same linear as wq8_small (at most 32 tokens, K multiple of 64, x rows and w 16-byte aligned) with the same kernel choice, hence the
-// same values bit for bit; no scratch arguments and no allocation of any kind: shapes that run the ring kernel need no scratch at all,
-// the others keep their K-split partial sums and tile counters in the library's own static device buffer.
+// same values bit for bit; no scratch arguments and no allocation of any kind: the digit planes, partial sums and tile counters that
+// wq8_small takes from its caller live in the library's own static device buffer.
 // Returns -5 when the shape's scratch would not fit that buffer (use wq8_small with caller scratch then); other codes as wq8_small.
 // Calls share the one buffer per device: two calls whose kernels may overlap on the GPU (different streams, or one stream of a graph with
 // parallel branches) race on it -- keep them on one stream, or give the others caller scratch through wq8_small.  The buffer keeps what
-// the last call left in it; the counters are cleared on the stream in front of every launch, the slots are written before they are read.
+// the last call left in it; the counters are cleared on the stream in front of every launch, everything else is written before it is read.
 WQ_API int wq8_small_static(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
                             void* y, int m, int n, int k, int dtype, int sms, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (k <= 0 || k % 64 || m > 32 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -2;
     if (dtype != 0 && dtype != 1) return -1;
-    const int rows = plan_bulk(m, n, k, sms);  // the ring kernel: no scratch at all
-    if (rows && dtype == 0) return launch_bulk<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
-    if (rows) return launch_bulk<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
-    const StreamPlan p = plan_stream(n, k, sms, true);
+    // how much scratch the kernel wq8_small would pick needs
+    int64_t counter_bytes = 0;
+    const int64_t tensor_core_bytes = tensor_core_scratch(m, n, k, sms, &counter_bytes);
+    const int rows = tensor_core_bytes ? 0 : plan_bulk(m, n, k, sms);
+    const DirectPlan p = plan_direct(m, n, k, sms, true);
+    int64_t slot_bytes = tensor_core_bytes;
+    if (!tensor_core_bytes && !rows && p.splits > 1) {
+        slot_bytes = direct_slot_bytes(p);
+        counter_bytes = 4 * int64_t(p.ctas);
+    }
     float* slots = nullptr;
     int* counters = nullptr;
-    if (p.splits > 1) {
-        const int64_t outputs = int64_t(8 / p.wk) * tokens_blocks(m) * 8 * 16;
-        const int64_t slot_bytes = int64_t(p.ctas) * p.splits * outputs * 4, counter_bytes = 4 * int64_t(p.ctas);
+    if (slot_bytes) {
         if (slot_bytes > kStaticSlotBytes || counter_bytes > kStaticCounterBytes) return -5;
         int error = 0;
         unsigned char* scratch = static_scratch_address(&error);
@@ -1016,6 +941,9 @@ WQ_API int wq8_small_static(const void* x, int64_t ldx, const int8_t* w, const f
         const cudaError_t cleared = cudaMemsetAsync(counters, 0, size_t(counter_bytes), stream);
         if (cleared != cudaSuccess) return int(cleared);
     }
-    if (dtype == 0) return launch_stream<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, slots, counters, stream);
-    return launch_stream<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, slots, counters, stream);
+    if (tensor_core_bytes) return stream_tc_launch(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, dtype, sms, slots, counters, stream);
+    if (rows && dtype == 0) return launch_bulk<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
+    if (rows) return launch_bulk<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, rows, sms, stream);
+    if (dtype == 0) return launch_direct<__half>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, slots, counters, stream);
+    return launch_direct<bf16>(x, ldx, w, sw, bias, residual, rscale, y, m, n, k, p, slots, counters, stream);
 }

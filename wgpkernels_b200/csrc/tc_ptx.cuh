@@ -124,6 +124,9 @@ WQ_DEVICE void tmem_load_16(uint32_t taddr, int* v) {
                  : "r"(taddr)
                  : "memory");
 }
+WQ_DEVICE void tmem_load_8(uint32_t taddr, int* v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];" : WQ_R4(v, 0), WQ_R4(v, 4) : "r"(taddr) : "memory");
+}
 #undef WQ_R4
 // Completes the loads issued before it (the toolchain tracks tcgen05.ld destinations until this instruction).
 WQ_DEVICE void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
