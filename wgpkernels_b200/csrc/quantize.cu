@@ -53,8 +53,8 @@ WQ_DEVICE void store_chunk_as_blocks(const float* v, int lane, int64_t row, int 
 // RMSNorm needs the row's sum of squares first: one CTA per row.  CPW > 0: the row (K <= 2048 * CPW) stays in registers, one read.
 // CPW == 0: any K, the row is read twice (the second read comes from L2).
 // Sum of squares: thread (warp w, lane l) accumulates fmaf(v, v, ss) over chunks w, w + 8, ... in order; then the ordered CTA sum.
-template <class T, int GROUP, int CPW>
-__global__ void __launch_bounds__(kRowThreads) quantize_blocks_rms(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, int m, int k,
+template <class T, int GROUP, int CPW, int VARIANT = 0>
+__global__ void __launch_bounds__(kRowThreads, VARIANT == 1 ? 5 : VARIANT == 3 ? 6 : 1) quantize_blocks_rms(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, int m, int k,
                                                                    int64_t ldx, const T* __restrict__ act_weight, float eps, RowShift shift) {
     __shared__ float slots[8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(kRowThreads) quantize_blocks_rms(const T* __re
         for (int i = 0; i < CPW; ++i) {
             const int col = (warp + 8 * i) * kChunk + lane * 8;
             load_eight(src + col, v[i], col < k);
-            weight_raw[i] = (act_weight && col < k) ? __ldg(reinterpret_cast<const uint4*>(act_weight + col)) : make_uint4(0u, 0u, 0u, 0u);
+            if (VARIANT < 2) weight_raw[i] = (act_weight && col < k) ? __ldg(reinterpret_cast<const uint4*>(act_weight + col)) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
         for (int i = 0; i < CPW; ++i)
@@ -83,6 +83,7 @@ __global__ void __launch_bounds__(kRowThreads) quantize_blocks_rms(const T* __re
         for (int i = 0; i < CPW; ++i) {
             const int base = (warp + 8 * i) * kChunk;
             if (base < k) {  // warp-uniform
+                if (VARIANT >= 2) weight_raw[i] = act_weight ? __ldg(reinterpret_cast<const uint4*>(act_weight + base + lane * 8)) : make_uint4(0u, 0u, 0u, 0u);
                 float w[8];
                 unpack_pair<T>(weight_raw[i].x, w[0], w[1]);
                 unpack_pair<T>(weight_raw[i].y, w[2], w[3]);
@@ -294,6 +295,7 @@ static int persistent_ctas(int64_t warps_of_work) {
     return int(ctas < cap ? (ctas < 1 ? 1 : ctas) : cap);
 }
 
+int g_rms_variant = 0;
 template <class T, int GROUP, int ACT>
 static int launch_blocks(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, const void* act_weight, float eps, const RowShift& shift,
                          cudaStream_t stream) {
@@ -302,6 +304,9 @@ static int launch_blocks(const void* x, int8_t* q, float* scale, int m, int k, i
     if constexpr (ACT == kActRms) {
         if (k <= 2048) quantize_blocks_rms<T, GROUP, 1><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
         else if (k <= 4096) quantize_blocks_rms<T, GROUP, 2><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
+        else if (k <= 8192 && g_rms_variant == 1) quantize_blocks_rms<T, GROUP, 4, 1><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
+        else if (k <= 8192 && g_rms_variant == 2) quantize_blocks_rms<T, GROUP, 4, 2><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
+        else if (k <= 8192 && g_rms_variant == 3) quantize_blocks_rms<T, GROUP, 4, 3><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
         else if (k <= 8192) quantize_blocks_rms<T, GROUP, 4><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
         else if (k <= 16384) quantize_blocks_rms<T, GROUP, 8><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
         else quantize_blocks_rms<T, GROUP, 0><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
@@ -468,6 +473,8 @@ WQ_API int wq8_quantize_at(const void* x, int8_t* hi, int8_t* lo, float* scale, 
                            const void* act_weight, float eps, const long long* counter, long long first, long long step, cudaStream_t stream) {
     return quantize_entry(x, hi, lo, scale, m, k, ldx, dtype, group, act, act_weight, eps, RowShift{counter, first, step}, stream);
 }
+
+WQ_API void wq8_debug_rms_variant(int v) { wq::g_rms_variant = v; }
 
 WQ_API int wq8_transform_rows(const void* x, void* out, int m, int k, int64_t ldx, int dtype, int group, int act, const void* act_weight, float eps,
                               cudaStream_t stream) {

@@ -52,6 +52,9 @@ template <int TB> struct TcShape {
 // of (run, token), 0 for empty slots.  One warp per (token slot, run), 4 values per lane.
 template <class T, int TB>
 __global__ void __launch_bounds__(256) split_digits(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ digits, float* __restrict__ scales, int m, int k) {
+    // the stream kernel that follows may start (its set-up and its weight loads do not depend on the digits); it waits for this grid
+    // to finish before it touches them
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int lane = threadIdx.x & 31, runs = k / kTcRun;
     const int unit = blockIdx.x * 8 + (threadIdx.x >> 5);
     constexpr int kRows = TcShape<TB>::kDigitRows, kSlots = kRows == 3 * TB ? TB : kRows - 2 * TB;  // TB = 8: 16 slots cover the padding rows
@@ -152,6 +155,10 @@ stream_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
+
+    // Launched with programmatic stream serialization behind the digit split: everything above overlapped its tail; from here on the
+    // digits and the scales are read.  (Without that launch attribute the instruction returns at once.)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // this CTA's share of the (tile, K block) pairs
     const long long total = (long long)p.tiles * p.kblocks, ctas = gridDim.x;
@@ -346,8 +353,19 @@ static int launch_tc_shape(const T* x, int64_t ldx, const int8_t* w, const float
     const int runs = k / kTcRun, units = runs * (TB == 8 ? 16 : TB);
     split_digits<T, TB><<<(units + 7) / 8, 256, 0, stream>>>(x, ldx, digits, scales, m, k);
     TcParams p{scales, sw, bias, residual, rscale, y, slots, counters, m, n, k, (n + kTcChannels - 1) / kTcChannels, runs};
-    kernel<<<plan.ctas, kTcThreads, S::kSmemBytes, stream>>>(map_w, map_d, p);
-    return int(cudaGetLastError());
+    // programmatic dependent launch: the stream kernel's set-up runs under the split's tail
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(plan.ctas);
+    config.blockDim = dim3(kTcThreads);
+    config.dynamicSmemBytes = S::kSmemBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    const cudaError_t launched = cudaLaunchKernelEx(&config, kernel, map_w, map_d, p);
+    return int(launched != cudaSuccess ? launched : cudaGetLastError());
 }
 
 // x (m, K) in T, already transformed; workspace: digits, then scales, then slots (plan sizes, each rounded up to 256 bytes); counters zeroed.

@@ -34,6 +34,7 @@ EXACT_ROWS, LINE_ROWS, SMALL_ROWS = 64, 2, 16            # untimed choices (CUDA
 # 'block' on long inputs); here 'exact' accumulates over all of K in tensor memory and has no per-block work on the CUDA cores, which
 # makes it as fast as 'block' on video-length inputs (measured on B200), so those are timed as well.
 LINE_MAX_ROWS, SMALL_MAX_ROWS, DECIDE_MAX_ROWS = 4, 32, 1 << 17
+PLANES_MAX_ROWS = 4  # few-token calls of at most this many tokens run the digit-plane mma.sync kernel, larger ones wq8_small (tcgen05)
 ACTS = {None: 0, "rms_norm": 1, "swiglu": 2, "gelu": 3}
 ABI = 11
 _COUNTERS = 1024
@@ -487,11 +488,12 @@ def gemm(a, a_lo, sa, b, sb, bias, out_dtype, split=None, variant=None, out=None
 
 
 def _stream_planes(lib, x, weight, scale, bias, residual, residual_scale, y):
-    """At most 8 tokens: the activations split into INT8 digit planes (exact to 2^-14 of the largest of every 128 values), the weights on
+    """A few tokens: the activations split into INT8 digit planes (exact to 2^-14 of the largest of every 128 values), the weights on
     INT8 tensor cores as they are.  False when the shape or the alignment is not this kernel's."""
     m, k = x.shape
     n, sms = weight.shape[0], _sm_count(x.device)
-    if m > 8 or x.stride(0) % 4 or x.data_ptr() % 8 or weight.data_ptr() % 16:
+    # up to PLANES_MAX_ROWS tokens this kernel is the fastest (measured on B200); above, wq8_small's tcgen05 kernel is
+    if m > PLANES_MAX_ROWS or x.stride(0) % 4 or x.data_ptr() % 8 or weight.data_ptr() % 16:
         return False
     size = lib.wq8_stream_planes_workspace(m, n, k, sms)
     if not size:
