@@ -72,8 +72,8 @@ template <int MODE, int BN, bool WIDE, int PARTS> struct Shape {
     static constexpr bool kWide = WIDE && kEpiColumns >= 64;
     static constexpr int kStoreTile = kWide ? 32 * 64 * 2 : 32 * 32 * 2;
     static constexpr int kStoreBytes = kDrainWarps * kStoreTile;
-    // Column parameters of the tile being finished (weight scale as FP32, bias and residual scale in the output type), shared by the drain warps.
-    static constexpr int kParamBytes = BN * 8;
+    // Column parameters of the tile being finished (weight scale and bias as FP32, residual scale in the output type), shared by the drain warps.
+    static constexpr int kParamBytes = BN * 10;
     static constexpr int kBarrierBytes = 384;
     static constexpr int kRoom = 227 * 1024 - kStoreBytes - kRingBytes - kParamBytes - kBarrierBytes;
     static constexpr int kStages = kRoom / kStageBytes > 6 ? 6 : kRoom / kStageBytes;
@@ -116,13 +116,27 @@ struct WeightMaps { CUtensorMap map[kMaxSegments]; };
 
 struct TileCoord { int m0, n0, segment; };
 // Bands of 16 row tiles are swept over all column tiles, so the CTAs running together share a few A bands and B tiles in L2.
+// Every role computes this once per tile, between two tiles' work: the one general division goes through a reciprocal (exact for the
+// tile counts of any launch, far below 2^24), full bands split by shifts, a single weight has segment 0.
 template <int BN> WQ_DEVICE TileCoord tile_origin(int t, int tiles_m, int tiles_n, int seg_tiles) {
     constexpr int kBand = 16;
-    const int width = kBand * tiles_n, first = (t / width) * kBand;
+    const int width = kBand * tiles_n;
+    int band = __float2int_rz(__int2float_rn(t) * __frcp_rn(__int2float_rn(width)));
+    int within = t - band * width;
+    if (within < 0) { --band; within += width; }
+    if (within >= width) { ++band; within -= width; }
+    const int first = band * kBand;
     const int rows = min(tiles_m - first, kBand);
-    const int column_tile = (t % width) / rows;
-    const int segment = column_tile / seg_tiles;
-    return {(first + (t % width) % rows) * kBM, (column_tile - segment * seg_tiles) * BN, segment};
+    int column_tile, row_tile;
+    if (rows == kBand) {
+        column_tile = within >> 4;
+        row_tile = within & (kBand - 1);
+    } else {
+        column_tile = within / rows;
+        row_tile = within - column_tile * rows;
+    }
+    const int segment = column_tile < seg_tiles ? 0 : column_tile / seg_tiles;
+    return {(first + row_tile) * kBM, (column_tile - segment * seg_tiles) * BN, segment};
 }
 
 WQ_DEVICE float2 as_pair(int a, int b) { return make_float2(__int_as_float(a), __int_as_float(b)); }
@@ -146,8 +160,8 @@ gemm_i8_tc(const __grid_constant__ InputMaps in_maps, const __grid_constant__ We
     float* store_stage_generic = reinterpret_cast<float*>(smem + kStages * S::kStageBytes + S::kRingBytes);
     uint8_t* params = smem + kStages * S::kStageBytes + S::kRingBytes + S::kStoreBytes;
     float* param_sb = reinterpret_cast<float*>(params);
-    T* param_bias = reinterpret_cast<T*>(params + BN * 4);
-    T* param_rscale = reinterpret_cast<T*>(params + BN * 6);
+    float* param_bias = reinterpret_cast<float*>(params + BN * 4);
+    T* param_rscale = reinterpret_cast<T*>(params + BN * 8);
     uint64_t* bars = reinterpret_cast<uint64_t*>(params + S::kParamBytes);
     // barrier layout: full[6], empty[6], acc_full[4], acc_empty[4], ring_full[kScaleRing], ring_empty[kScaleRing], params_written,
     // params_consumed; then the TMEM slot and the abort flag
@@ -317,7 +331,7 @@ gemm_i8_tc(const __grid_constant__ InputMaps in_maps, const __grid_constant__ We
         // ---------------- column parameters: per tile for the write-out, per block for group-scaled weights ----------------
         // The write-out of a tile needs each column's weight scale, bias and residual scale.  Fetching them there would put a trip to
         // L2 (long, while the operand loads keep it busy) in front of every group of outputs; this warp puts them into shared memory
-        // one tile ahead instead: as FP32 weight scale, bias (0 if none) and residual scale (1 if none) in the output type.
+        // one tile ahead instead: weight scale and bias (0 if none) as FP32, residual scale (1 if none) in the output type.
         if constexpr (!DUMP) {
             const T* rscale = static_cast<const T*>(p.rscale);
             int slot = 0, tile_count = 0;
@@ -333,7 +347,7 @@ gemm_i8_tc(const __grid_constant__ InputMaps in_maps, const __grid_constant__ We
                     const int col = c.n0 + i;
                     const bool inside = col < p.n;
                     param_sb[i] = !S::kWGroup && inside ? __ldg(sb + col) : 0.f;
-                    param_bias[i] = bias && inside ? bias[col] : round_one<T>(0.f);
+                    param_bias[i] = bias && inside ? as_float(bias[col]) : 0.f;
                     param_rscale[i] = rscale && !p.window.span && inside ? rscale[col] : round_one<T>(1.f);
                 }
                 mbar_arrive(bar_params_written);
@@ -382,8 +396,9 @@ gemm_i8_tc(const __grid_constant__ InputMaps in_maps, const __grid_constant__ We
         int tile_count = 0;  // tiles this CTA has finished: the phase of the parameter hand-over barriers
         float sa_ahead[2] = {0.f, 0.f};
         bool sa_ahead_valid = false;
-        for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-            const TileCoord c = tile_origin<BN>(t, p.tiles_m, p.tiles_n, p.seg_tiles);
+        // the next tile's coordinates are worked out before this tile's write-out, where the arithmetic hides behind the stores
+        TileCoord c = tile_origin<BN>(blockIdx.x, p.tiles_m, p.tiles_n, p.seg_tiles), c_next = c;
+        for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, c = c_next) {
             const int row = c.m0 + quarter * 32 + lane;
             const bool row_ok = row < p.m;
             const int col0 = c.n0 + part * kEpi;
@@ -434,7 +449,11 @@ gemm_i8_tc(const __grid_constant__ InputMaps in_maps, const __grid_constant__ We
                             scale8[0] = s0.x; scale8[1] = s0.y; scale8[2] = s0.z; scale8[3] = s0.w;
                             scale8[4] = s1.x; scale8[5] = s1.y; scale8[6] = s1.z; scale8[7] = s1.w;
                         }
-                        load_eight_plain(param_bias + ct, bias8);
+                        {
+                            const float4 b0 = *reinterpret_cast<const float4*>(param_bias + ct), b1 = *reinterpret_cast<const float4*>(param_bias + ct + 4);
+                            bias8[0] = b0.x; bias8[1] = b0.y; bias8[2] = b0.z; bias8[3] = b0.w;
+                            bias8[4] = b1.x; bias8[5] = b1.y; bias8[6] = b1.z; bias8[7] = b1.w;
+                        }
 #pragma unroll
                         for (int e = 0; e < 8; ++e) out[e] = fmaf(v[j + e] * row_scale, scale8[e], bias8[e]);
                         if (res) {
@@ -501,6 +520,76 @@ gemm_i8_tc(const __grid_constant__ InputMaps in_maps, const __grid_constant__ We
                         }
                     }
                 }
+            };
+
+            // The common write-out: a tile that lies inside N, 16-byte accessible operands, one destination reached through its tensor map.
+            // Everything a chunk needs beside the accumulators sits in shared memory as FP32 (or arrives as `res`, four 16-byte pieces of the
+            // residual row requested a chunk ahead); the outputs are computed with two-wide FP32 instructions and rounded BEFORE the warp waits
+            // for the TMA unit to be done reading the staging tile of the previous chunk, so that wait hides behind the arithmetic.
+            // Same operations per output, in the same order, as `emit`: the bits do not depend on which of the two writes a tile.
+            const bool fast_tile = !S::kWide && p.vector_io && p.tma_y && p.destinations == 1 && c.n0 + BN <= p.n && !(rscale && p.window.span);
+            auto emit_fast = [&](const float2* a, int chunk, const uint4* res, bool has_res) {
+                const int ct = part * kEpi + chunk * 32;  // first column of the chunk within the tile
+                uint32_t packed[16];
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {  // eight columns
+                    float2 o[4];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        float2 v0 = a[4 * g + 2 * h], v1 = a[4 * g + 2 * h + 1];
+                        if constexpr (!S::kBlockScales) {
+                            v0 = __fmul2_rn(v0, make_float2(row_scale, row_scale));
+                            v1 = __fmul2_rn(v1, make_float2(row_scale, row_scale));
+                        }
+                        const float4 b = *reinterpret_cast<const float4*>(param_bias + ct + 8 * g + 4 * h);
+                        if constexpr (S::kWGroup) {
+                            o[2 * h] = __fadd2_rn(v0, make_float2(b.x, b.y));
+                            o[2 * h + 1] = __fadd2_rn(v1, make_float2(b.z, b.w));
+                        } else {
+                            const float4 w = *reinterpret_cast<const float4*>(param_sb + ct + 8 * g + 4 * h);
+                            o[2 * h] = __ffma2_rn(v0, make_float2(w.x, w.y), make_float2(b.x, b.y));
+                            o[2 * h + 1] = __ffma2_rn(v1, make_float2(w.z, w.w), make_float2(b.z, b.w));
+                        }
+                    }
+                    if (has_res) {
+                        const uint4 rs = *reinterpret_cast<const uint4*>(param_rscale + ct + 8 * g);
+                        const uint32_t rs_raw[4] = {rs.x, rs.y, rs.z, rs.w}, res_raw[4] = {res[g].x, res[g].y, res[g].z, res[g].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float2 scale2, res2;
+                            unpack_pair<T>(rs_raw[e], scale2.x, scale2.y);
+                            unpack_pair<T>(res_raw[e], res2.x, res2.y);
+                            o[e] = __ffma2_rn(o[e], scale2, res2);
+                        }
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) packed[4 * g + e] = pack_pair<T>(o[e].x, o[e].y);
+                }
+                // the TMA store that last read this warp's staging tile must be done with it
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                __syncwarp();
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    // row `lane` of the staging tile, 16-byte piece g at its place in the 64-byte swizzle
+                    const uint32_t piece = uint32_t(g) ^ ((uint32_t(lane) >> 1) & 3u);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_stage + lane * 64 + piece * 16), "r"(packed[4 * g]),
+                                 "r"(packed[4 * g + 1]), "r"(packed[4 * g + 2]), "r"(packed[4 * g + 3])
+                                 : "memory");
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&out_maps.map[c.segment]),
+                                 "r"(c.n0 + ct), "r"(c.m0 + quarter * 32), "r"(my_stage)
+                                 : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+            };
+            // 16-byte piece g of the 32 residual values that belong to chunk `chunk` of this thread's row (plain loads: y may be the residual)
+            const T* res_row = residual && row_ok ? residual + (out_shift + row) * p.ld_residual + col0 : nullptr;
+            auto fetch_residual = [&](int chunk, uint4* res) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) res[g] = *reinterpret_cast<const uint4*>(res_row + chunk * 32 + 8 * g);
             };
 
             if constexpr (S::kFold) {
@@ -616,12 +705,13 @@ gemm_i8_tc(const __grid_constant__ InputMaps in_maps, const __grid_constant__ We
                     if constexpr (kAccBuffers > 3) if (ok && kb + 3 < kblocks) ok = drain_block(std::integral_constant<int, 3>(), kb + 3);
                 }
                 if (!ok) break;
+                const int t_next = t + int(gridDim.x);
+                if (t_next < tiles) c_next = tile_origin<BN>(t_next, p.tiles_m, p.tiles_n, p.seg_tiles);
                 if constexpr (S::kBlockScales && !DUMP) {
                     // the first two block scales of this thread's row in the next tile: in flight while this tile is written out
-                    const int t_next = t + int(gridDim.x);
                     sa_ahead_valid = t_next < tiles;
                     if (sa_ahead_valid) {
-                        const int row_next = tile_origin<BN>(t_next, p.tiles_m, p.tiles_n, p.seg_tiles).m0 + quarter * 32 + lane;
+                        const int row_next = c_next.m0 + quarter * 32 + lane;
                         const float* next_row = sa + int64_t(row_next < p.m ? row_next : 0) * kblocks;
                         sa_ahead[0] = __ldg(next_row);
                         sa_ahead[1] = kblocks > 1 ? __ldg(next_row + 1) : 0.f;
@@ -629,6 +719,22 @@ gemm_i8_tc(const __grid_constant__ InputMaps in_maps, const __grid_constant__ We
                 }
                 if constexpr (!DUMP) {
                     if (!(ok = await_params())) break;
+                    if (fast_tile) {
+                        // the residual of a chunk is requested while the chunk before it is written out, where the registers allow it
+                        constexpr bool kResidualAhead = PARTS == 2 && !S::kWGroup;
+                        uint4 res[kResidualAhead ? 2 : 1][4];
+                        if (kResidualAhead && res_row) fetch_residual(0, res[0]);
+#pragma unroll
+                        for (int chunk = 0; chunk < kEpi / 32; ++chunk) {
+                            if constexpr (kResidualAhead) {
+                                if (res_row && chunk + 1 < kEpi / 32) fetch_residual(chunk + 1, res[(chunk + 1) & 1]);
+                                emit_fast(&accf[chunk * 16], chunk, res[chunk & 1], res_row != nullptr);
+                            } else {
+                                if (res_row) fetch_residual(chunk, res[0]);
+                                emit_fast(&accf[chunk * 16], chunk, res[0], res_row != nullptr);
+                            }
+                        }
+                    } else
 #pragma unroll
                     for (int chunk = 0; chunk < kEpi / 32; ++chunk) {
                         float v[32];
@@ -645,6 +751,7 @@ gemm_i8_tc(const __grid_constant__ InputMaps in_maps, const __grid_constant__ We
                 if (!(ok = __all_sync(0xffffffffu, wait_on(bar_acc_full + 8 * acc, acc_phase, abort_flag, kTimeoutTmemFull)))) break;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + lane_base + acc * S::kAccColumns + part * kEpi;
+                if (t + int(gridDim.x) < tiles) c_next = tile_origin<BN>(t + int(gridDim.x), p.tiles_m, p.tiles_n, p.seg_tiles);
                 if (!(ok = await_params())) break;
 #pragma unroll 1
                 for (int chunk = 0; chunk < kEpi / 32; ++chunk) {
@@ -664,7 +771,16 @@ gemm_i8_tc(const __grid_constant__ InputMaps in_maps, const __grid_constant__ We
                         __syncwarp();
                         if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
                     }
-                    emit(v, col0 + chunk * 32, chunk);
+                    if (fast_tile) {
+                        float2 pairs[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) pairs[j] = make_float2(v[2 * j], v[2 * j + 1]);
+                        uint4 res[4];
+                        if (res_row) fetch_residual(chunk, res);
+                        emit_fast(pairs, chunk, res, res_row != nullptr);
+                    } else {
+                        emit(v, col0 + chunk * 32, chunk);
+                    }
                 }
                 params_done();
                 if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1u; }

@@ -53,8 +53,8 @@ WQ_DEVICE void store_chunk_as_blocks(const float* v, int lane, int64_t row, int 
 // RMSNorm needs the row's sum of squares first: one CTA per row.  CPW > 0: the row (K <= 2048 * CPW) stays in registers, one read.
 // CPW == 0: any K, the row is read twice (the second read comes from L2).
 // Sum of squares: thread (warp w, lane l) accumulates fmaf(v, v, ss) over chunks w, w + 8, ... in order; then the ordered CTA sum.
-template <class T, int GROUP, int CPW, int VARIANT = 0>
-__global__ void __launch_bounds__(kRowThreads, VARIANT == 1 ? 5 : VARIANT == 3 ? 6 : 1) quantize_blocks_rms(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, int m, int k,
+template <class T, int GROUP, int CPW>
+__global__ void __launch_bounds__(kRowThreads, CPW > 0 && CPW <= 4 ? 6 : 1) quantize_blocks_rms(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, int m, int k,
                                                                    int64_t ldx, const T* __restrict__ act_weight, float eps, RowShift shift) {
     __shared__ float slots[8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -63,16 +63,12 @@ __global__ void __launch_bounds__(kRowThreads, VARIANT == 1 ? 5 : VARIANT == 3 ?
     const int kblocks = (k + kBlockK - 1) / kBlockK;
     float ss = 0.f;
     if constexpr (CPW > 0) {
-        // The row and this thread's slice of the RMSNorm weight are requested together, before the reduction: nothing is loaded
-        // between the barrier and the stores.
         static_assert(sizeof(T) == 2, "rms_norm takes 16-bit inputs");
         float v[CPW][8];
-        uint4 weight_raw[CPW];
 #pragma unroll
         for (int i = 0; i < CPW; ++i) {
             const int col = (warp + 8 * i) * kChunk + lane * 8;
             load_eight(src + col, v[i], col < k);
-            if (VARIANT < 2) weight_raw[i] = (act_weight && col < k) ? __ldg(reinterpret_cast<const uint4*>(act_weight + col)) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
         for (int i = 0; i < CPW; ++i)
@@ -83,12 +79,14 @@ __global__ void __launch_bounds__(kRowThreads, VARIANT == 1 ? 5 : VARIANT == 3 ?
         for (int i = 0; i < CPW; ++i) {
             const int base = (warp + 8 * i) * kChunk;
             if (base < k) {  // warp-uniform
-                if (VARIANT >= 2) weight_raw[i] = act_weight ? __ldg(reinterpret_cast<const uint4*>(act_weight + base + lane * 8)) : make_uint4(0u, 0u, 0u, 0u);
+                // the RMSNorm weights of the chunk come from L1 / L2 when they are needed: held from before the reduction they would cost the
+                // registers that let six CTAs share an SM (the kernel is bound by instruction issue: occupancy is what it needs)
+                const uint4 raw = (act_weight && base + lane * 8 < k) ? __ldg(reinterpret_cast<const uint4*>(act_weight + base + lane * 8)) : make_uint4(0u, 0u, 0u, 0u);
                 float w[8];
-                unpack_pair<T>(weight_raw[i].x, w[0], w[1]);
-                unpack_pair<T>(weight_raw[i].y, w[2], w[3]);
-                unpack_pair<T>(weight_raw[i].z, w[4], w[5]);
-                unpack_pair<T>(weight_raw[i].w, w[6], w[7]);
+                unpack_pair<T>(raw.x, w[0], w[1]);
+                unpack_pair<T>(raw.y, w[2], w[3]);
+                unpack_pair<T>(raw.z, w[4], w[5]);
+                unpack_pair<T>(raw.w, w[6], w[7]);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[i][j] = v[i][j] * inv_rms * (act_weight ? w[j] : 1.f);
                 rotate_chunk<GROUP>(v[i]);
@@ -145,8 +143,10 @@ template <bool HILO> WQ_DEVICE void store_row_codes(const float* v, float inv, i
     if (HILO) *reinterpret_cast<uint2*>(lo + offset) = make_uint2(pack_bytes(l[0], l[1], l[2], l[3]), pack_bytes(l[4], l[5], l[6], l[7]));
 }
 
+// Rows of up to 8192 values: five CTAs per SM (at most 51 registers per thread) -- these kernels are bound by instruction issue and by
+// the latency of their two CTA-wide reductions, so resident warps count for more than registers.
 template <class T, int GROUP, bool HILO, int ACT, int CPW>
-__global__ void __launch_bounds__(kRowThreads) quantize_rows(const T* __restrict__ x, int8_t* __restrict__ hi, int8_t* __restrict__ lo,
+__global__ void __launch_bounds__(kRowThreads, CPW > 0 && CPW <= 4 ? 5 : 1) quantize_rows(const T* __restrict__ x, int8_t* __restrict__ hi, int8_t* __restrict__ lo,
                                                              float* __restrict__ scale, int k, int64_t ldx, const T* __restrict__ act_weight, float eps,
                                                              RowShift shift) {
     __shared__ float sum_slots[8], max_slots[8];
@@ -295,7 +295,6 @@ static int persistent_ctas(int64_t warps_of_work) {
     return int(ctas < cap ? (ctas < 1 ? 1 : ctas) : cap);
 }
 
-int g_rms_variant = 0;
 template <class T, int GROUP, int ACT>
 static int launch_blocks(const void* x, int8_t* q, float* scale, int m, int k, int64_t ldx, const void* act_weight, float eps, const RowShift& shift,
                          cudaStream_t stream) {
@@ -304,9 +303,6 @@ static int launch_blocks(const void* x, int8_t* q, float* scale, int m, int k, i
     if constexpr (ACT == kActRms) {
         if (k <= 2048) quantize_blocks_rms<T, GROUP, 1><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
         else if (k <= 4096) quantize_blocks_rms<T, GROUP, 2><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
-        else if (k <= 8192 && g_rms_variant == 1) quantize_blocks_rms<T, GROUP, 4, 1><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
-        else if (k <= 8192 && g_rms_variant == 2) quantize_blocks_rms<T, GROUP, 4, 2><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
-        else if (k <= 8192 && g_rms_variant == 3) quantize_blocks_rms<T, GROUP, 4, 3><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
         else if (k <= 8192) quantize_blocks_rms<T, GROUP, 4><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
         else if (k <= 16384) quantize_blocks_rms<T, GROUP, 8><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
         else quantize_blocks_rms<T, GROUP, 0><<<m, kRowThreads, 0, stream>>>(src, q, scale, m, k, ldx, aw, eps, shift);
@@ -473,8 +469,6 @@ WQ_API int wq8_quantize_at(const void* x, int8_t* hi, int8_t* lo, float* scale, 
                            const void* act_weight, float eps, const long long* counter, long long first, long long step, cudaStream_t stream) {
     return quantize_entry(x, hi, lo, scale, m, k, ldx, dtype, group, act, act_weight, eps, RowShift{counter, first, step}, stream);
 }
-
-WQ_API void wq8_debug_rms_variant(int v) { wq::g_rms_variant = v; }
 
 WQ_API int wq8_transform_rows(const void* x, void* out, int m, int k, int64_t ldx, int dtype, int group, int act, const void* act_weight, float eps,
                               cudaStream_t stream) {
