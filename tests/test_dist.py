@@ -83,7 +83,7 @@ def _rank_main(rank, world_size, port, failures):
             return out
 
         fused_layer = wdist.ShardedLinear.from_full(c.weight, c.scale, c.bias, linear=writing_linear)
-        fused_layer.symmetric_output = lambda m, dtype, device: (views[rank], views, torch.zeros(1))
+        fused_layer.symmetric_output = lambda m, dtype, device, which=0: (views[rank], views, torch.zeros(1))
         returned = fused_layer(c.x, gather="fused", out=torch.empty(1))  # a caller's `out` is ignored: the result is the layer's buffer
         assert returned is views[rank]
         try:  # the fused gather never times paths: a few-token path (or none given and a tuner picking one) is refused

@@ -85,7 +85,8 @@ class ShardedLinear:
             from wgpkernels_b200 import int8
             self.linear = int8.linear
         self._gathered = None
-        self._symmetric = {}  # (M, dtype) -> (own buffer, views of every rank's buffer, barrier token)
+        self._symmetric = {}  # (M, dtype, which of the two alternating sets) -> (own buffer, views of every rank's buffer, barrier token)
+        self._fused_calls = {}  # (M, dtype) -> calls of fused() so far
 
     @classmethod
     def from_full(cls, weight, scale, bias=None, group=None, linear=None):
@@ -100,9 +101,10 @@ class ShardedLinear:
         """This rank's output columns (M, N_local).  residual / residual_scale: the rank's own columns."""
         return self.linear(x, self.weight, self.scale, self.bias, residual=residual, residual_scale=residual_scale, **kwargs)
 
-    def symmetric_output(self, m, dtype, device):
-        """(own (M, N) buffer, [view of rank r's buffer for every r], token) in symmetric memory; a collective call the first time."""
-        key = (m, dtype)
+    def symmetric_output(self, m, dtype, device, which=0):
+        """(own (M, N) buffer, [view of rank r's buffer for every r], token) in symmetric memory; a collective call the first time.
+        which: 0 or 1, the two sets of buffers fused() alternates between."""
+        key = (m, dtype, which)
         if key not in self._symmetric:
             import torch.distributed._symmetric_memory as symmetric_memory
             own = symmetric_memory.empty((m, self.n_total), dtype=dtype, device=device)
@@ -112,15 +114,18 @@ class ShardedLinear:
         return self._symmetric[key][:3]
 
     def fused(self, x, residual=None, residual_scale=None, **kwargs):
-        """(M, N) on every rank, each rank's GEMM writing its columns into all ranks' buffers.  The result is this layer's own buffer for
-        (M, dtype): it is overwritten by the next call with the same M.  residual / residual_scale: the rank's own columns, (M, N / g)
-        with any row stride and (N / g)."""
+        """(M, N) on every rank, each rank's GEMM writing its columns into all ranks' buffers.  The result is one of this layer's two
+        buffers for (M, dtype), used in turn: it stays valid until the call AFTER the next one with the same M is made (work that reads
+        it must be on the stream before that call).  One 4-byte all-reduce per call orders everything: it ends the call, so it follows
+        the rank's stores and, on the same stream, whatever the rank enqueued earlier -- the readers of the other buffer set included;
+        nobody starts the next call's stores into that other set before every rank has reached this point.
+        residual / residual_scale: the rank's own columns, (M, N / g) with any row stride and (N / g)."""
         mode = kwargs.setdefault("mode", "block")
         if mode not in ("block", "exact", "row"):
             raise ValueError(f"the fused gather runs the 'block', 'exact' or 'row' path (every rank the same one), not {mode!r}")
-        own, views, token = self.symmetric_output(x.shape[0], x.dtype, x.device)
-        # every rank has finished reading the previous contents of the buffers (this rank's kernels that read them precede on its stream)
-        dist.all_reduce(token, group=self.group)
+        calls = self._fused_calls.get((x.shape[0], x.dtype), 0)
+        self._fused_calls[(x.shape[0], x.dtype)] = calls + 1
+        own, views, token = self.symmetric_output(x.shape[0], x.dtype, x.device, calls & 1)
         # own buffer first, then the peers starting from the next rank, so that the ranks do not all store to the same GPU at once
         order = [(self.rank + d) % self.world_size for d in range(self.world_size)]
         outputs = [views[r][:, self.start:self.stop] for r in order]

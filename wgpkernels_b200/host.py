@@ -71,21 +71,59 @@ class HostLinear:
         return out_host
 
 
-def _shared_pinned(path, shape, dtype, create):
-    """A host tensor backed by a file of shared memory that every process of the node maps, registered with CUDA so that copies to
-    and from it are asynchronous (the same bytes in all processes: the ranks of a node fill and read one activation together)."""
+def _shared_mapping(path, shape, dtype, create):
+    """A host tensor backed by a file of shared memory that every process of the node maps (the same bytes in all processes: the
+    ranks of a node fill and read one activation together).  create: make the file, sparse -- no page exists until somebody writes."""
     count = 1
     for extent in shape:
         count *= extent
-    size = count * torch.empty((), dtype=dtype).element_size()
     if create:
         with open(path, "wb") as handle:
-            handle.truncate(size)
-    tensor = torch.from_file(path, shared=True, size=count, dtype=dtype).view(shape)
-    code = torch.cuda.cudart().cudaHostRegister(tensor.data_ptr(), size, 0)
+            handle.truncate(count * torch.empty((), dtype=dtype).element_size())
+    return torch.from_file(path, shared=True, size=count, dtype=dtype).view(shape)
+
+
+def _register(tensor):
+    """Pins the pages of a host tensor where they are and makes copies to and from it asynchronous."""
+    code = torch.cuda.cudart().cudaHostRegister(tensor.data_ptr(), tensor.numel() * tensor.element_size(), 0)
     if int(code) != 0:
         raise RuntimeError(f"cudaHostRegister failed ({code})")
-    return tensor
+
+
+def _cpus_near(device):
+    """The CPUs of the NUMA node a GPU hangs on (from sysfs), limited to those this process may run on; None when unknown."""
+    import os
+    try:
+        props = torch.cuda.get_device_properties(device)
+        address = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{address}/local_cpulist") as handle:
+            text = handle.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            first, _, last = part.partition("-")
+            cpus.update(range(int(first), int(last or first) + 1))
+        cpus &= os.sched_getaffinity(0)
+        return cpus or None
+    except (OSError, ValueError, AttributeError, RuntimeError, AssertionError):
+        return None
+
+
+def _touch_near(device, tensors):
+    """Writes zeros into host tensors that have no pages yet while the calling thread runs on the CPUs next to `device`: the kernel
+    places a page on the NUMA node of the thread that first writes it, so the rows a GPU copies end up in the memory of its own socket
+    and its PCIe traffic does not cross the link between the sockets.  The thread's CPU affinity is put back afterwards."""
+    import os
+    before = os.sched_getaffinity(0)
+    near = _cpus_near(device)
+    try:
+        if near:
+            os.sched_setaffinity(0, near)
+        import ctypes
+        for tensor in tensors:  # contiguous row bands; written by this very thread (a parallel fill would touch from other threads)
+            ctypes.memset(tensor.data_ptr(), 0, tensor.numel() * tensor.element_size())
+    finally:
+        if near:
+            os.sched_setaffinity(0, before)
 
 
 class ShardedHostLinear:
@@ -107,12 +145,19 @@ class ShardedHostLinear:
         self.start, self.stop = min(rank * per_rank, rows), min((rank + 1) * per_rank, rows)
         self._paths = [f"/dev/shm/wgpkernels_b200_{tag}_{name}" for name in ("x", "y")]
         shapes = ((rows, k), (rows, weight.shape[0]))
+        # rank 0 makes the (sparse) files, every rank maps them, writes its own band first -- which places that band's pages in the host
+        # memory next to its GPU -- and only then are the pages pinned, by every rank, where they lie
         if rank == 0:
-            self.x, self.y = (_shared_pinned(path, shape, dtype, True) for path, shape in zip(self._paths, shapes))
+            self.x, self.y = (_shared_mapping(path, shape, dtype, True) for path, shape in zip(self._paths, shapes))
         if world > 1:
             dist.barrier(group)
         if rank != 0:
-            self.x, self.y = (_shared_pinned(path, shape, dtype, False) for path, shape in zip(self._paths, shapes))
+            self.x, self.y = (_shared_mapping(path, shape, dtype, False) for path, shape in zip(self._paths, shapes))
+        _touch_near(torch.cuda.current_device(), (self.x[self.start:self.stop], self.y[self.start:self.stop]))
+        if world > 1:
+            dist.barrier(group)
+        _register(self.x)
+        _register(self.y)
         self.inner = HostLinear(weight, scale, bias, chunk_rows=chunk_rows)
         self.h2d_bytes = self.x.numel() * self.x.element_size()
         self.d2h_bytes = self.y.numel() * self.y.element_size()
