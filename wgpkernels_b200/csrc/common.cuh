@@ -81,8 +81,13 @@ template <class T> WQ_DEVICE void load_eight_plain(const T* p, float* v) {
     unpack_pair<T>(raw.w, v[6], v[7]);
 }
 
+// Four INT8 codes (each already within [-128, 127]) into one word, a in the lowest byte: two packing conversions
+// (cvt.pack: the two converted values go to the low half, the third operand's low half moves up).
 WQ_DEVICE uint32_t pack_bytes(int a, int b, int c, int d) {
-    return (uint32_t(a) & 0xffu) | ((uint32_t(b) & 0xffu) << 8) | ((uint32_t(c) & 0xffu) << 16) | (uint32_t(d) << 24);
+    uint32_t high, word;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(high) : "r"(d), "r"(c), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(word) : "r"(b), "r"(a), "r"(high));
+    return word;
 }
 
 // ---- input operations, FP32 (the expression shapes fix the rounding: they are part of the numerical contract) ----
@@ -117,17 +122,24 @@ template <class T> WQ_DEVICE void scale_by_rms(float* v, float inv_rms, const T*
 
 WQ_DEVICE float inverse_rms(float sum_squares, int k, float eps) { return 1.f / sqrtf(sum_squares / float(k) + eps); }
 
-// Sum over the 256 threads of a CTA in a fixed order: xor-butterfly inside each warp, then warps 0..7 in turn.
-WQ_DEVICE float cta_sum_ordered(float v, float* slots8) {
+// 1 / rms of a row from the threads' partial sums of squares, summed in a fixed order (xor-butterfly inside each warp, then warps 0..7 in
+// turn); the sum over the warps, the division, the square root and the reciprocal are done by the first warp alone and handed to the others through shared
+// memory (slots9[8]) -- a second barrier instead of some fifty instructions in each of the other seven warps.
+WQ_DEVICE float cta_inverse_rms(float v, float* slots9, int k, float eps) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-    if (lane == 0) slots8[warp] = v;
+    if (lane == 0) slots9[warp] = v;
     __syncthreads();
-    float total = slots8[0];
+    if (warp == 0) {
+        float total = slots9[0];
 #pragma unroll
-    for (int w = 1; w < 8; ++w) total += slots8[w];
-    return total;
+        for (int w = 1; w < 8; ++w) total += slots9[w];
+        const float result = inverse_rms(total, k, eps);
+        if (lane == 0) slots9[8] = result;
+    }
+    __syncthreads();
+    return slots9[8];
 }
 
 WQ_DEVICE float cta_max(float v, float* slots8) {

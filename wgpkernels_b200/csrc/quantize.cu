@@ -22,14 +22,11 @@ WQ_DEVICE void store_chunk_as_blocks(const float* v, int lane, int64_t row, int 
     for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
 #pragma unroll
     for (int d = 8; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));  // stays inside each half warp
-    // the two IEEE divisions of a block are done by its first lane only; the other fifteen receive the reciprocal scale
-    float inv = 0.f;
-    if ((lane & 15) == 0) {
-        inv = amax > 0.f ? 127.f / amax : 0.f;
-        const int block = base / kBlockK + (lane >> 4);
-        if (block < kblocks) scale[row * kblocks + block] = amax * group_norm<GROUP>() / 127.f;
-    }
-    inv = __shfl_sync(0xffffffffu, inv, lane & 16);
+    // every lane holds its block's absmax: all of them do the division (the instructions issue once per warp either way; a branch for the
+    // first lane of a block and a shuffle back would only add to them), the block's first lane stores the scale
+    const float inv = amax > 0.f ? 127.f / amax : 0.f;
+    const int block = base / kBlockK + (lane >> 4);
+    if ((lane & 15) == 0 && block < kblocks) scale[row * kblocks + block] = amax * group_norm<GROUP>() / 127.f;
     const int col = base + lane * 8;
     if (col < k) {
         int c[8];
@@ -56,7 +53,7 @@ WQ_DEVICE void store_chunk_as_blocks(const float* v, int lane, int64_t row, int 
 template <class T, int GROUP, int CPW>
 __global__ void __launch_bounds__(kRowThreads, CPW > 0 && CPW <= 4 ? 6 : 1) quantize_blocks_rms(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, int m, int k,
                                                                    int64_t ldx, const T* __restrict__ act_weight, float eps, RowShift shift) {
-    __shared__ float slots[8];
+    __shared__ float slots[9];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t row = blockIdx.x;
     const T* src = first_row(x, ldx, shift) + row * ldx;
@@ -74,7 +71,7 @@ __global__ void __launch_bounds__(kRowThreads, CPW > 0 && CPW <= 4 ? 6 : 1) quan
         for (int i = 0; i < CPW; ++i)
 #pragma unroll
             for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
-        const float inv_rms = inverse_rms(cta_sum_ordered(ss, slots), k, eps);
+        const float inv_rms = cta_inverse_rms(ss, slots, k, eps);
 #pragma unroll
         for (int i = 0; i < CPW; ++i) {
             const int base = (warp + 8 * i) * kChunk;
@@ -100,7 +97,7 @@ __global__ void __launch_bounds__(kRowThreads, CPW > 0 && CPW <= 4 ? 6 : 1) quan
 #pragma unroll
             for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
         }
-        const float inv_rms = inverse_rms(cta_sum_ordered(ss, slots), k, eps);
+        const float inv_rms = cta_inverse_rms(ss, slots, k, eps);
         for (int base = warp * kChunk; base < k; base += 8 * kChunk) {
             float v[8];
             const bool valid = base + lane * 8 < k;
@@ -149,7 +146,7 @@ template <class T, int GROUP, bool HILO, int ACT, int CPW>
 __global__ void __launch_bounds__(kRowThreads, CPW > 0 && CPW <= 4 ? 5 : 1) quantize_rows(const T* __restrict__ x, int8_t* __restrict__ hi, int8_t* __restrict__ lo,
                                                              float* __restrict__ scale, int k, int64_t ldx, const T* __restrict__ act_weight, float eps,
                                                              RowShift shift) {
-    __shared__ float sum_slots[8], max_slots[8];
+    __shared__ float sum_slots[9], max_slots[8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t row = blockIdx.x;
     const T* src = first_row(x, ldx, shift) + row * ldx;
@@ -167,7 +164,7 @@ __global__ void __launch_bounds__(kRowThreads, CPW > 0 && CPW <= 4 ? 5 : 1) quan
             for (int i = 0; i < CPW; ++i)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
-            const float inv_rms = inverse_rms(cta_sum_ordered(ss, sum_slots), k, eps);
+            const float inv_rms = cta_inverse_rms(ss, sum_slots, k, eps);
 #pragma unroll
             for (int i = 0; i < CPW; ++i) {
                 const int col = (warp + 8 * i) * kChunk + lane * 8;
@@ -198,7 +195,7 @@ __global__ void __launch_bounds__(kRowThreads, CPW > 0 && CPW <= 4 ? 5 : 1) quan
 #pragma unroll
                 for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
             }
-            inv_rms = inverse_rms(cta_sum_ordered(ss, sum_slots), k, eps);
+            inv_rms = cta_inverse_rms(ss, sum_slots, k, eps);
         }
         for (int base = warp * kChunk; base < k; base += 8 * kChunk) {
             float v[8];
@@ -227,7 +224,7 @@ __global__ void __launch_bounds__(kRowThreads, CPW > 0 && CPW <= 4 ? 5 : 1) quan
 template <class T, int GROUP, int ACT>
 __global__ void __launch_bounds__(kRowThreads) transform_rows(const T* __restrict__ x, T* __restrict__ out, int k, int64_t ldx,
                                                               const T* __restrict__ act_weight, float eps) {
-    __shared__ float slots[8];
+    __shared__ float slots[9];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t row = blockIdx.x;
     const T* src = x + row * ldx;
@@ -240,7 +237,7 @@ __global__ void __launch_bounds__(kRowThreads) transform_rows(const T* __restric
 #pragma unroll
             for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
         }
-        inv_rms = inverse_rms(cta_sum_ordered(ss, slots), k, eps);
+        inv_rms = cta_inverse_rms(ss, slots, k, eps);
     }
     constexpr float norm = group_norm<GROUP>();
     // gridDim.y CTAs share a row when no row statistic is needed: with one or a few rows every warp then has one chunk and one trip to
