@@ -474,7 +474,20 @@ def main():
     sampler = ClockSampler(local_rank) if rank == 0 else None
 
     # ---- value: inputs resident in HBM ------------------------------------------------------------------------------------
-    total_ms = timed(lambda: step(g.x), args.steps)
+    # One GPU: the quantizer and the GEMM are timed inside these very calls (events recorded from linear()'s stage hook).
+    inner = []
+    if world == 1:
+        def hooked_step():
+            begin = torch.cuda.Event(enable_timing=True)
+            begin.record()
+            stamps = [begin]
+            wq.stage_hook = lambda tag: (stamps.append(torch.cuda.Event(enable_timing=True)), stamps[-1].record())
+            step(g.x)
+            wq.stage_hook = None
+            inner.append(stamps)
+        total_ms = timed(hooked_step, args.steps)
+    else:
+        total_ms = timed(lambda: step(g.x), args.steps)
 
     # ---- kernel breakdown: events around the quantizer and the GEMM of every step -------------------------------------------
     marks = []
@@ -491,9 +504,13 @@ def main():
         e2.record()
         marks.append((e0, e1, e2))
 
-    timed(split_step, args.steps)
-    quant_ms = sum(a.elapsed_time(b) for a, b, _ in marks) / len(marks)
-    gemm_ms = sum(b.elapsed_time(d) for _, b, d in marks) / len(marks)
+    if inner and all(len(stamps) == 3 for stamps in inner):
+        quant_ms = sum(a.elapsed_time(b) for a, b, _ in inner) / len(inner)
+        gemm_ms = sum(b.elapsed_time(d) for _, b, d in inner) / len(inner)
+    else:  # several ranks (the step's GEMM also stores to the peers), or more than one band of rows: a pass of its own
+        timed(split_step, args.steps)
+        quant_ms = sum(a.elapsed_time(b) for a, b, _ in marks) / len(marks)
+        gemm_ms = sum(b.elapsed_time(d) for _, b, d in marks) / len(marks)
     status = wq.debug_status()
 
     # ---- several ranks: is the gathered output the unsharded linear's?  and the forms without an exchange -----------------------

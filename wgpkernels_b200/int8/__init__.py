@@ -594,6 +594,11 @@ def _chunk_rows(k, mode):
     return max(SCRATCH_BYTES // per_row // 128, 1) * 128
 
 
+# Measurement aid: a callable that linear() calls with "quantized" after a band's activation quantizer has been enqueued and with
+# "multiplied" after its GEMM (a benchmark records CUDA events there, so that the kernels are timed inside the very calls it times).
+stage_hook = None
+
+
 def _gemm_path(x, weight, scale, bias, group, mode, act=None, act_weight=None, eps=0.0, residual=None, residual_scale=None, out=None):
     """'exact', 'block' or 'row': quantize a band of rows, multiply it, next band.  out: a tensor, or a list of destinations."""
     m, n = x.shape[0], weight.shape[0]
@@ -604,8 +609,12 @@ def _gemm_path(x, weight, scale, bias, group, mode, act=None, act_weight=None, e
     for first in range(0, m, band):
         rows = slice(first, min(first + band, m))
         prepared = prepare(x[rows], group, mode, act, act_weight, eps)
+        if stage_hook is not None:
+            stage_hook("quantized")
         linear_prepared(prepared, weight, scale, bias, residual[rows] if residual is not None else None, residual_scale,
                         [t[rows] for t in out] if several else out[rows])
+        if stage_hook is not None:
+            stage_hook("multiplied")
         del prepared  # the band's codes go back to the allocator before the next band is quantized
     return out
 
