@@ -204,6 +204,39 @@ template <int GROUP> WQ_DEVICE void rotate_chunk(float* v) {
 }
 template <int GROUP> __host__ __device__ constexpr float group_norm() { return GROUP == 256 ? 0.0625f : GROUP == 64 ? 0.125f : GROUP == 16 ? 0.25f : 1.f; }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------------------------------
+// A kernel launched with launch_after_previous() may start while the kernel before it on the stream is still running: what it does
+// before dependency_wait() (set-up, requests for data the previous kernel does not write) overlaps that kernel's tail; after the wait the
+// previous kernel has finished and its writes are visible.  The previous kernel lets the next one start early with dependents_may_start();
+// without it the next one starts when the previous one ends, as usual.  Data the previous kernel wrote is read with ordinary loads (below),
+// never through the read-only path, whose contract is that nobody writes the data while the kernel runs.
+WQ_DEVICE void dependents_may_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+WQ_DEVICE void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+WQ_DEVICE uint4 load_16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+WQ_DEVICE uint2 load_8(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+template <class... Params, class... Args>
+inline cudaError_t launch_after_previous(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, Params(args)...);
+}
+
 // ---- device status word (bounded waits report here instead of trapping) ----------------------------------------------
 // gemm_tc.cu: tensor map of a (rows, row_bytes) row-major byte matrix with boxes of box_rows rows x box_bytes bytes (at most 256), no
 // swizzle, zero fill outside; false when the driver entry point is missing or refuses the description.

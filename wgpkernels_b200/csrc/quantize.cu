@@ -225,6 +225,7 @@ template <class T, int GROUP, int ACT>
 __global__ void __launch_bounds__(kRowThreads) transform_rows(const T* __restrict__ x, T* __restrict__ out, int k, int64_t ldx,
                                                               const T* __restrict__ act_weight, float eps) {
     __shared__ float slots[9];
+    dependents_may_start();  // a few-token linear follows: its digit split may be set up while these rows are transformed
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t row = blockIdx.x;
     const T* src = x + row * ldx;

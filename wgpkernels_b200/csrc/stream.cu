@@ -416,15 +416,19 @@ constexpr int kPlaneTokens = 8;  // token slots of the planes (one MMA column bl
 
 // planes: (8 tokens, 3, K) int8, scales: (K / 128, 8 tokens) float = 2^(E-7).  One warp per token and run, 4 values per lane.
 template <class T>
-__global__ void __launch_bounds__(256) split_planes(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ planes, float* __restrict__ scales, int m,
+__global__ void __launch_bounds__(256) split_planes(const T* x, int64_t ldx, int8_t* __restrict__ planes, float* __restrict__ scales, int m,
                                                     int k) {
+    // the stream kernel behind this one may start (its set-up and its first weight requests do not depend on the planes); this kernel
+    // itself may have started under the tail of the one that produced x
+    dependents_may_start();
+    dependency_wait();
     const int lane = threadIdx.x & 31, runs = k / kPlaneRun;
     const int unit = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (unit >= runs * kPlaneTokens) return;
     const int token = unit % kPlaneTokens, run = unit / kPlaneTokens;
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (token < m) {
-        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + int64_t(token) * ldx + run * kPlaneRun + 4 * lane));
+        const uint2 raw = load_8(x + int64_t(token) * ldx + run * kPlaneRun + 4 * lane);
         unpack_pair<T>(raw.x, v[0], v[1]);
         unpack_pair<T>(raw.y, v[2], v[3]);
     }
@@ -461,8 +465,8 @@ WQ_DEVICE void mma_s8_16x8x32(int* d, uint32_t a0, uint32_t a1, uint32_t a2, uin
 }
 
 template <class T, int ROWS>
-__global__ void __launch_bounds__(kBulkThreads, 1) stream_planes(const __grid_constant__ CUtensorMap map_w, const int8_t* __restrict__ planes,
-                                                                 const float* __restrict__ scales, const float* __restrict__ sw, const T* __restrict__ bias,
+__global__ void __launch_bounds__(kBulkThreads, 1) stream_planes(const __grid_constant__ CUtensorMap map_w, const int8_t* planes,
+                                                                 const float* scales, const float* __restrict__ sw, const T* __restrict__ bias,
                                                                  const T* residual, const T* __restrict__ rscale, T* y, int m, int n, int k) {
     constexpr int MT = 1;
     using S = BulkShape<MT, ROWS>;
@@ -542,6 +546,8 @@ __global__ void __launch_bounds__(kBulkThreads, 1) stream_planes(const __grid_co
 
     long long requested = 0;
     for (; requested < total && requested < kStages; ++requested) request();
+    // the ring's first stages of weights are on their way; the digit planes and their scales exist once the split kernel has finished
+    dependency_wait();
     bool ok = true;
     long long landed = 0;
     int slot = 0;
@@ -559,13 +565,13 @@ __global__ void __launch_bounds__(kBulkThreads, 1) stream_planes(const __grid_co
             for (int run = 0; run < RUNS; ++run) {
                 const int k0 = segment * SEG + run * kPlaneRun;
                 const bool inside = k0 < k && g < m;  // token slots past M hold zeros: not fetched (their MMA columns are never stored)
-                scale[run] = k0 < k ? __ldg(reinterpret_cast<const float2*>(my_scales + (k0 / kPlaneRun) * kPlaneTokens)) : make_float2(0.f, 0.f);
+                const uint2 scale_bits = k0 < k ? load_8(my_scales + (k0 / kPlaneRun) * kPlaneTokens) : make_uint2(0u, 0u);
+                scale[run] = make_float2(__uint_as_float(scale_bits.x), __uint_as_float(scale_bits.y));
 #pragma unroll
                 for (int p = 0; p < 3; ++p)
 #pragma unroll
                     for (int piece = 0; piece < 2; ++piece)
-                        digits[run][p][piece] = inside ? __ldg(reinterpret_cast<const uint4*>(plane0 + int64_t(p) * k + k0 + piece * kStreamChunk))
-                                                       : make_uint4(0u, 0u, 0u, 0u);
+                        digits[run][p][piece] = inside ? load_16(plane0 + int64_t(p) * k + k0 + piece * kStreamChunk) : make_uint4(0u, 0u, 0u, 0u);
             }
             if (ok) ok = __all_sync(0xffffffffu, bulk_wait(bars + 8 * slot, parity, gave_up));
             if (ok) {
@@ -745,8 +751,10 @@ static int launch_planes_shape(const int8_t* planes, const float* scales, const 
     CUtensorMap map_w;
     if (!make_byte_matrix_map(&map_w, w, n, k, S::kSegment, ROWS)) return int(cudaErrorNotSupported);
     const int items = (n + ROWS - 1) / ROWS;
-    kernel<<<items < sms ? items : sms, kBulkThreads, S::kSmemBytes, stream>>>(map_w, planes, scales, sw, bias, residual, rscale, y, m, n, k);
-    return int(cudaGetLastError());
+    // launched behind the split: set-up and the first weight requests run under its tail
+    const cudaError_t launched = launch_after_previous(kernel, dim3(items < sms ? items : sms), dim3(kBulkThreads), size_t(S::kSmemBytes), stream, map_w, planes, scales,
+                                                       sw, bias, residual, rscale, y, m, n, k);
+    return int(launched != cudaSuccess ? launched : cudaGetLastError());
 }
 
 // The digit planes of the activations into `workspace`, then the INT8 tensor-core kernel.
@@ -756,7 +764,8 @@ static int launch_planes(const void* x, int64_t ldx, const int8_t* w, const floa
     int8_t* planes = static_cast<int8_t*>(workspace);
     float* scales = reinterpret_cast<float*>(planes + int64_t(kPlaneTokens) * 3 * k);
     const int units = (k / kPlaneRun) * kPlaneTokens;
-    split_planes<T><<<(units + 7) / 8, 256, 0, stream>>>(static_cast<const T*>(x), ldx, planes, scales, m, k);
+    const cudaError_t split = launch_after_previous(split_planes<T>, dim3((units + 7) / 8), dim3(256), size_t(0), stream, static_cast<const T*>(x), ldx, planes, scales, m, k);
+    if (split != cudaSuccess) return int(split);
     auto b = static_cast<const T*>(bias), r = static_cast<const T*>(residual), rs = static_cast<const T*>(rscale);
     auto out = static_cast<T*>(y);
     if (sms <= 0) sms = 148;

@@ -51,10 +51,11 @@ template <int TB> struct TcShape {
 // digits: (3 TB [padded to 32 rows for TB = 8], K) int8, row p * TB + t = plane p of token slot t; scales: (K / 128, TB) float = 2^(E-7)
 // of (run, token), 0 for empty slots.  One warp per (token slot, run), 4 values per lane.
 template <class T, int TB>
-__global__ void __launch_bounds__(256) split_digits(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ digits, float* __restrict__ scales, int m, int k) {
-    // the stream kernel that follows may start (its set-up and its weight loads do not depend on the digits); it waits for this grid
-    // to finish before it touches them
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+__global__ void __launch_bounds__(256) split_digits(const T* x, int64_t ldx, int8_t* __restrict__ digits, float* __restrict__ scales, int m, int k) {
+    // the stream kernel that follows may start (its set-up and its first weight loads do not depend on the digits); it waits for this
+    // grid to finish before it touches them.  This kernel itself may have started under the tail of the one that produced x.
+    dependents_may_start();
+    dependency_wait();
     const int lane = threadIdx.x & 31, runs = k / kTcRun;
     const int unit = blockIdx.x * 8 + (threadIdx.x >> 5);
     constexpr int kRows = TcShape<TB>::kDigitRows, kSlots = kRows == 3 * TB ? TB : kRows - 2 * TB;  // TB = 8: 16 slots cover the padding rows
@@ -66,7 +67,7 @@ __global__ void __launch_bounds__(256) split_digits(const T* __restrict__ x, int
     }
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (token < m) {
-        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + int64_t(token) * ldx + run * kTcRun + 4 * lane));
+        const uint2 raw = load_8(x + int64_t(token) * ldx + run * kTcRun + 4 * lane);
         unpack_pair<T>(raw.x, v[0], v[1]);
         unpack_pair<T>(raw.y, v[2], v[3]);
     }
@@ -156,9 +157,9 @@ stream_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
 
-    // Launched with programmatic stream serialization behind the digit split: everything above overlapped its tail; from here on the
-    // digits and the scales are read.  (Without that launch attribute the instruction returns at once.)
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Launched with programmatic stream serialization behind the digit split: everything above overlapped its tail, and so do the
+    // producer's first weight loads; each role waits for the split to finish before it touches the digits or the scales.  (Without
+    // that launch attribute the wait returns at once.)
 
     // this CTA's share of the (tile, K block) pairs
     const long long total = (long long)p.tiles * p.kblocks, ctas = gridDim.x;
@@ -170,7 +171,21 @@ stream_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (long long pair = begin; pair < end && ok; ++pair) {
+            // the ring's first fill: the weights go out at once, the digits of the same stages once the split has finished
+            const long long first_fill = end - begin < kStages ? end - begin : kStages;
+            for (long long i = 0; i < first_fill; ++i) {
+                const long long pair = begin + i;
+                const int tile = int(pair / p.kblocks), kb = int(pair - (long long)tile * p.kblocks);
+                mbar_expect_tx(bar_full + 8 * int(i), S::kStageBytes);
+                tma_load_2d(smem_u32(smem + int(i) * S::kStageBytes), &map_w, bar_full + 8 * int(i), kb * kTcRun, tile * kTcChannels);
+            }
+            dependency_wait();
+            for (long long i = 0; i < first_fill; ++i) {
+                const int kb = int((begin + i) % p.kblocks);
+                tma_load_2d(smem_u32(smem + int(i) * S::kStageBytes) + S::kWeightBytes, &map_d, bar_full + 8 * int(i), kb * kTcRun, 0);
+            }
+            if (first_fill == kStages) phase = 1u; else stage = int(first_fill);
+            for (long long pair = begin + first_fill; pair < end && ok; ++pair) {
                 const int tile = int(pair / p.kblocks), kb = int(pair - (long long)tile * p.kblocks);
                 if (!(ok = tc_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag))) break;
                 const uint32_t full = bar_full + 8 * stage, dst = smem_u32(smem + stage * S::kStageBytes);
@@ -211,6 +226,7 @@ stream_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         }
     } else if (warp >= 4) {
         // ---------------- drain: one thread per output channel of the tile ----------------
+        dependency_wait();  // the scales of the runs come from the split
         const int quarter = warp & 3;
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
         const int thread = quarter * 32 + lane;  // channel of the tile
@@ -231,7 +247,10 @@ stream_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 // the powers of two of this run's tokens: requested before the wait (every lane the same addresses: one transaction each)
                 float4 scale4[TB / 4];
 #pragma unroll
-                for (int i = 0; i < TB / 4; ++i) scale4[i] = __ldg(reinterpret_cast<const float4*>(p.scales + (long long)kb * TB) + i);
+                for (int i = 0; i < TB / 4; ++i) {
+                    const uint4 bits = load_16(p.scales + (long long)kb * TB + 4 * i);
+                    scale4[i] = make_float4(__uint_as_float(bits.x), __uint_as_float(bits.y), __uint_as_float(bits.z), __uint_as_float(bits.w));
+                }
                 const int buffer = int(block % kAcc);
                 if (!(ok = tc_wait(bar_acc_full + 8 * buffer, uint32_t(block / kAcc) & 1u, abort_flag))) break;
                 tc_fence_after();
@@ -351,20 +370,11 @@ static int launch_tc_shape(const T* x, int64_t ldx, const int8_t* w, const float
     if (!make_swizzled_byte_map(&map_w, w, n, k, kTcChannels) || !make_swizzled_byte_map(&map_d, digits, S::kDigitRows, k, S::kDigitRows))
         return int(cudaErrorNotSupported);
     const int runs = k / kTcRun, units = runs * (TB == 8 ? 16 : TB);
-    split_digits<T, TB><<<(units + 7) / 8, 256, 0, stream>>>(x, ldx, digits, scales, m, k);
+    const cudaError_t split = launch_after_previous(split_digits<T, TB>, dim3((units + 7) / 8), dim3(256), size_t(0), stream, x, ldx, digits, scales, m, k);
+    if (split != cudaSuccess) return int(split);
     TcParams p{scales, sw, bias, residual, rscale, y, slots, counters, m, n, k, (n + kTcChannels - 1) / kTcChannels, runs};
-    // programmatic dependent launch: the stream kernel's set-up runs under the split's tail
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(plan.ctas);
-    config.blockDim = dim3(kTcThreads);
-    config.dynamicSmemBytes = S::kSmemBytes;
-    config.stream = stream;
-    cudaLaunchAttribute attribute;
-    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute.val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = &attribute;
-    config.numAttrs = 1;
-    const cudaError_t launched = cudaLaunchKernelEx(&config, kernel, map_w, map_d, p);
+    // behind the split: the stream kernel's set-up and first weight loads run under the split's tail
+    const cudaError_t launched = launch_after_previous(kernel, dim3(plan.ctas), dim3(kTcThreads), size_t(S::kSmemBytes), stream, map_w, map_d, p);
     return int(launched != cudaSuccess ? launched : cudaGetLastError());
 }
 
