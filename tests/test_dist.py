@@ -77,6 +77,8 @@ def _rank_main(rank, world_size, port, failures):
 
         def writing_linear(x, weight, scale, bias, residual=None, residual_scale=None, out=None, **kwargs):
             result = cpu_linear(x, weight, scale, bias, residual=residual, residual_scale=residual_scale, **kwargs)
+            if out is None:
+                return result
             for target in out:
                 order.append(next(i for i, view in enumerate(views) if view.data_ptr() == target.data_ptr() - target.storage_offset() * target.element_size()))
                 target.copy_(result)
@@ -92,6 +94,12 @@ def _rank_main(rank, world_size, port, failures):
         except ValueError:
             pass
         assert order == [(rank + d) % world_size for d in range(world_size)]
+        # 'auto': few rows (a weight stream, nothing to store from) go through the all-gather, more rows through the fused epilogue
+        calls = len(order)
+        wdist.FUSED_MIN_ROWS = 8
+        assert torch.equal(fused_layer(c.x[:4], gather="auto"), full[:4]) and len(order) == calls
+        assert fused_layer(c.x, gather="auto") is views[rank] and len(order) == calls + world_size
+        assert fused_layer.policy(32760)["best_ranks"] >= 1
         for view in views:
             assert torch.equal(view[:, fused_layer.start:fused_layer.stop], full[:, fused_layer.start:fused_layer.stop])
             untouched = torch.ones(256, dtype=torch.bool)

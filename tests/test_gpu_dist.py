@@ -27,7 +27,7 @@ for name, rows in (("c1", 1000), ("c2", 700), ("c4", 520)):
     cut = slice(layer.start, layer.stop)
     residual = None if full.residual is None else full.residual[:, cut]
     rscale = None if full.residual_scale is None else full.residual_scale[cut].contiguous()
-    for gather in ("fused", "full", "fused"):
+    for gather in ("fused", "full", "fused", "auto", "fused"):  # alternating buffer sets: the result of a call outlives the next call
         got = layer(full.x, gather=gather, mode="block", act=full.act, act_weight=full.act_weight, eps=full.eps, residual=residual,
                     residual_scale=rscale)
         torch.cuda.synchronize()
@@ -40,6 +40,9 @@ for name, rows in (("c1", 1000), ("c2", 700), ("c4", 520)):
         got = layer(full.x, gather="fused", mode=mode, act=full.act, act_weight=full.act_weight, eps=full.eps, residual=residual, residual_scale=rscale)
         torch.cuda.synchronize()
         assert torch.equal(got, expected), (name, mode, rank)
+    few = layer(full.x[:4], gather="auto", mode="lines", act=full.act, act_weight=full.act_weight, eps=full.eps)  # few tokens: the all-gather route
+    torch.cuda.synchronize()
+    assert few.shape == (4, expected.shape[1])
     try:
         layer(full.x[:4], gather="fused", mode="lines")
         raise AssertionError("few-token paths must be refused by the fused gather")

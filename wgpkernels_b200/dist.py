@@ -59,6 +59,9 @@ def worth_sharding(m, n, k, world_size, tops=MEASURED_TOPS, link_gbs=MEASURED_LI
             "best_ranks": best, "best_ms": step_ms(best), "bound": "nvlink" if gather_ms > gemm_ms / world_size else "tensor"}
 
 
+FUSED_MIN_ROWS = 32  # up to here the linear is a few-token weight stream (lines / small): no tile epilogue to store from
+
+
 @dataclass
 class ShardedLinear:
     """The rank's slice of one INT8 linear.  weight (N_local, K) int8, scale (N_local,) or (N_local, ceil(K / 128)) fp32, bias (N_local,).
@@ -101,6 +104,11 @@ class ShardedLinear:
         """This rank's output columns (M, N_local).  residual / residual_scale: the rank's own columns."""
         return self.linear(x, self.weight, self.scale, self.bias, residual=residual, residual_scale=residual_scale, **kwargs)
 
+    def policy(self, m):
+        """worth_sharding() for this layer's shape and group size at m rows: the estimate of what sharding gains, the number of ranks
+        that would serve a replicated output best, and what bounds it."""
+        return worth_sharding(m, self.n_total, self.weight.shape[1], self.world_size)
+
     def symmetric_output(self, m, dtype, device, which=0):
         """(own (M, N) buffer, [view of rank r's buffer for every r], token) in symmetric memory; a collective call the first time.
         which: 0 or 1, the two sets of buffers fused() alternates between."""
@@ -137,10 +145,14 @@ class ShardedLinear:
     def __call__(self, x, gather="full", broadcast_input=False, residual=None, residual_scale=None, **kwargs):
         """gather: 'full' -> (M, N) on every rank; 'blocked' -> (g, M, N / g), rank-major (what the all-gather delivers, no extra copy);
         'fused' -> (M, N) on every rank without a collective on the data (see fused(); block / exact / row paths only);
+        'auto' -> (M, N) on every rank by the cheaper of the two routes: 'fused' for more than FUSED_MIN_ROWS rows on a path the fused
+        epilogue runs ('block' when none is named), the NCCL all-gather ('full') for the few-token paths, whose outputs are a few KB;
         None -> the local (M, N / g) slice only.  residual / residual_scale: the rank's own columns.
         broadcast_input: x is valid on rank 0 only and is broadcast first."""
         if broadcast_input and self.world_size > 1:
             dist.broadcast(x, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0, group=self.group)
+        if gather == "auto":
+            gather = "fused" if x.shape[0] > FUSED_MIN_ROWS and kwargs.get("mode", "block") in ("block", "exact", "row") else "full"
         if gather == "fused" and self.world_size > 1:
             return self.fused(x, residual=residual, residual_scale=residual_scale, **kwargs)
         if gather == "fused":
