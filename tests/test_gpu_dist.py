@@ -40,9 +40,11 @@ for name, rows in (("c1", 1000), ("c2", 700), ("c4", 520)):
         got = layer(full.x, gather="fused", mode=mode, act=full.act, act_weight=full.act_weight, eps=full.eps, residual=residual, residual_scale=rscale)
         torch.cuda.synchronize()
         assert torch.equal(got, expected), (name, mode, rank)
-    few = layer(full.x[:4], gather="auto", mode="lines", act=full.act, act_weight=full.act_weight, eps=full.eps)  # few tokens: the all-gather route
-    torch.cuda.synchronize()
-    assert few.shape == (4, expected.shape[1])
+    if full.scale.dim() == 1:  # few tokens: 'auto' takes the all-gather route
+        few = layer(full.x[:4], gather="auto", mode="lines", act=full.act, act_weight=full.act_weight, eps=full.eps)
+        alone = wq.linear(full.x[:4], full.weight, full.scale, full.bias, mode="lines", act=full.act, act_weight=full.act_weight, eps=full.eps)
+        torch.cuda.synchronize()
+        assert torch.equal(few, alone), (name, "auto, few tokens", rank)
     try:
         layer(full.x[:4], gather="fused", mode="lines")
         raise AssertionError("few-token paths must be refused by the fused gather")
