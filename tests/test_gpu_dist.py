@@ -44,7 +44,8 @@ for name, rows in (("c1", 1000), ("c2", 700), ("c4", 520)):
         few = layer(full.x[:4], gather="auto", mode="lines", act=full.act, act_weight=full.act_weight, eps=full.eps)
         alone = wq.linear(full.x[:4], full.weight, full.scale, full.bias, mode="lines", act=full.act, act_weight=full.act_weight, eps=full.eps)
         torch.cuda.synchronize()
-        assert torch.equal(few, alone), (name, "auto, few tokens", rank)
+        # the few-token kernels split K by the shape of N: a slice's sums are added in another order than the whole matrix's
+        assert float((few.float() - alone.float()).norm()) <= 1e-3 * float(alone.float().norm()), (name, "auto, few tokens", rank)
     try:
         layer(full.x[:4], gather="fused", mode="lines")
         raise AssertionError("few-token paths must be refused by the fused gather")
