@@ -163,6 +163,12 @@ def test_row_bands_through_small_scratch(wq, monkeypatch):
         in_place = c.residual.clone()
         banded = wq.linear(c.x, c.weight, c.scale, c.bias, mode=mode, residual=in_place, out=in_place, **kwargs)
         assert banded.data_ptr() == in_place.data_ptr() and torch.equal(banded, whole), mode
+        # the stage hook (what the benchmark records its events from) is called once per band and stage, in order
+        tags = []
+        monkeypatch.setattr(wq, "stage_hook", tags.append)
+        wq.linear(c.x, c.weight, c.scale, c.bias, mode=mode, residual=c.residual, **kwargs)
+        assert tags == ["quantized", "multiplied"] * 3, tags
+        monkeypatch.setattr(wq, "stage_hook", None)
         wide = [torch.zeros((700, c.n + 64), dtype=c.x.dtype, device="cuda") for _ in range(2)]
         wq.linear(c.x, c.weight, c.scale, c.bias, mode=mode, residual=c.residual, out=[t[:, 32:32 + c.n] for t in wide], **kwargs)
         for t in wide:
