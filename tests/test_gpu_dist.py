@@ -31,7 +31,12 @@ for name, rows in (("c1", 1000), ("c2", 700), ("c4", 520)):
         got = layer(full.x, gather=gather, mode="block", act=full.act, act_weight=full.act_weight, eps=full.eps, residual=residual,
                     residual_scale=rscale)
         torch.cuda.synchronize()
-        assert got.shape == expected.shape and torch.equal(got, expected), (name, gather, rank, float((got.float() - expected.float()).abs().max()))
+        if got.shape != expected.shape or not torch.equal(got, expected):  # say where: whose columns, which rows
+            bad = (got != expected).nonzero()
+            width = expected.shape[1] // dist.get_world_size()
+            raise AssertionError((name, gather, rank, "mismatches", int(bad.shape[0]), "columns of ranks", sorted(set((bad[:, 1] // width).tolist())),
+                                  "rows", sorted(set(bad[:, 0].tolist()))[:12], "columns", sorted(set(bad[:, 1].tolist()))[:12],
+                                  "max difference", float((got.float() - expected.float()).abs().max())))
     for mode in ("exact", "row"):
         if full.scale.dim() == 2 and mode == "row":
             continue

@@ -78,10 +78,20 @@ template <int MODE, int BN, bool WIDE, int PARTS> struct Shape {
     static constexpr int kRoom = 227 * 1024 - kStoreBytes - kRingBytes - kParamBytes - kBarrierBytes;
     // The per-block modes are bound by their drain warps, not by the operand feed: three stages serve them better than four (measured:
     // +1.5 % with K = 5120, +5 % with K = 3072; two stages lose 8 %), `row` wants all it can get (four: 2910 TOPS, three: 2710).
-    static constexpr int kStageLimit = kFold ? 3 : 6;
-    static constexpr int kStages = kRoom / kStageBytes > kStageLimit ? kStageLimit : kRoom / kStageBytes;
+    static constexpr int kStageLimit = kFold && BN == 256 ? 3 : 6;  // the 128-channel tiles (smaller stages) keep theirs
+    static constexpr int kStagesThatFit = kRoom / kStageBytes > kStageLimit ? kStageLimit : kRoom / kStageBytes;
+    // with more than two accumulator buffers the per-block modes take an even number of stages (see the assertion below)
+    static constexpr int kStages = kFold && kAccBuffers > 2 ? kStagesThatFit / 2 * 2 : kStagesThatFit;
     static constexpr int kSmemBytes = kStages * kStageBytes + kRingBytes + kStoreBytes + kParamBytes + kBarrierBytes;
     static_assert(kAccBuffers >= 1 && kStages >= 2, "tile does not fit");
+    // Per-block modes have two MMA issuers taking the blocks in turn.  With an even number of stages a stage always meets the same
+    // issuer.  With an odd one its consecutive fills are awaited by different threads, and a thread that asks for a fill before the one
+    // before it has even landed would take the barrier's parity test (one phase bit) for passed.  A thread gets its accumulator buffer
+    // back only after the drain has consumed the block kAccBuffers before -- whose operands, and those of every earlier block, had to
+    // land first -- at a tile boundary up to 2 kAccBuffers - 1 before, since every tile starts at buffer 0 --, so the fill kStages
+    // blocks back has certainly landed when kStages >= 2 kAccBuffers - 1: three stages with two buffers.  (Three stages with the four
+    // buffers of the 128-channel tiles did produce a few wrong sums when loads landed out of order under NVLink traffic.)
+    static_assert(!kFold || kStages % 2 == 0 || kStages >= 2 * kAccBuffers - 1, "an odd number of stages needs that many to be safe with two issuers");
     static_assert(kEpiColumns % 32 == 0, "a drain thread works on chunks of 16 or 32 and writes out chunks of 32 columns");
 };
 
