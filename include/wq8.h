@@ -107,7 +107,10 @@ int wq8_gemm_at(const int8_t* a, const int8_t* a_lo, const float* sa, const int8
  * slots / counters: scratch of the sizes wq8_small_workspace() reports (slots 256-byte aligned); counters zero on entry,
  * left zero.  With scratch and K a multiple of 128 the linear runs on tcgen05 (the activations as INT8 digit planes --
  * see wq8_stream_planes for their accuracy --, K ranges shared over all SMs, partial sums added in a fixed order);
- * without scratch (NULL) on the kernels that need none.  Replaces int8_gemm.cu:1752-1759 and :1693-1697. */
+ * without scratch (NULL) on the kernels that need none.  The digit split and the stream kernel of a call are launched with
+ * programmatic stream serialization: each may start under the tail of the kernel before it on the stream (wq8_transform_rows lets
+ * them) and waits for that kernel to finish before it reads what it wrote; callers need to do nothing.
+ * Replaces int8_gemm.cu:1752-1759 and :1693-1697. */
 int wq8_small(const void* x, int64_t ldx, const int8_t* w, const float* sw, const void* bias, const void* residual, const void* rscale,
               void* y, int m, int n, int k, int dtype, int sms, float* slots, int* counters, wq8_stream_t stream);
 void wq8_small_workspace(int m, int n, int k, int sms, int64_t* sizes);
